@@ -16,7 +16,9 @@ taken until tokens arrive), so that several partial prefills can never exhaust
 the pool between them (qil/cache.py:1-6,58-77).  A request admitted without a
 limit reserves nothing and grows until the free list is empty (trace replay).
 
-Layout of a group's storage: ``[member, page, 2 (K,V), kv_head, slot, head_dim]``.
+Layout of a group's storage: ``[member, page, 2 (K,V), kv_head, slot, head_dim]``; where values have
+another size than keys, ``[member, page, kv_head * slot * (head_dim + v_head_dim)]``: a page's key rows
+``[kv_head, slot, head_dim]`` followed by its value rows ``[kv_head, slot, v_head_dim]``.
 """
 from __future__ import annotations
 
@@ -40,7 +42,7 @@ class OutOfPages(RuntimeError):
 @dataclass
 class KVCacheView:
     """What an attention-like mixer gets: its layer's pages and the request block tables."""
-    pages: torch.Tensor          # [num_pages, 2, kv_heads, page_size, head_dim]
+    pages: torch.Tensor          # [num_pages, 2, kv_heads, page_size, head_dim] (or flat pages, see the module's text)
     block_table: torch.Tensor    # int32 [max_requests, table_width]; -1 where no page is held
     page_size: int
     window: int
@@ -56,8 +58,11 @@ class _KVGroup:
     def __init__(self, spec, members, num_pages, page_size, max_requests, table_width, dtype, device):
         self.spec, self.members = spec, list(members)
         self.capacity, self.page_size = int(num_pages), int(page_size)
-        self.storage = torch.empty((len(self.members), num_pages, 2, spec.kv_heads, page_size, spec.head_dim),
-                                   dtype=dtype, device=device)
+        if spec.value_dim == spec.head_dim:
+            shape = (len(self.members), num_pages, 2, spec.kv_heads, page_size, spec.head_dim)
+        else:     # a page's key rows, then its value rows
+            shape = (len(self.members), num_pages, spec.kv_heads * page_size * (spec.head_dim + spec.value_dim))
+        self.storage = torch.empty(shape, dtype=dtype, device=device)
         self.free = deque(range(num_pages))
         self.tables: dict = {}       # request -> list of page ids by logical page index (-1: given back)
         self.first_live: dict = {}   # request -> first logical page index still needed

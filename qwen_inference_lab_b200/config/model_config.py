@@ -118,3 +118,85 @@ def read_config_json(directory) -> dict:
     if not isinstance(data, dict):
         raise ConfigError(f"{path} must hold a JSON object")
     return data
+
+
+_MIXER_KEYS = {
+    "attention": {"heads", "kv_heads", "dim", "vdim", "scale"},
+    "gla": {"heads", "dim", "vdim", "tau"},
+}
+
+
+class VirulixConfig:
+    """Virulix: a decoder whose layers are listed one by one in config.json.
+
+    ``vocab``, ``width``, ``norm.eps`` and ``layers``: each layer names its mixer (``type``: ``attention`` or
+    ``gla``), the mixer's sizes and constants (``mixer``) and its feed-forward (``mlp``: ``dense``, ``moe``
+    or null).  The configuration is kept as the dictionary it came in; this class checks it and answers
+    the few questions the engine asks.  The design has no position table, so ``max_positions`` (not a key
+    of the design; 2**20 unless given) only bounds what a request may ask for: the cache is the limit.
+    """
+    architecture = "Virulix"
+    model_type = "virulix"
+
+    def __init__(self, data: dict):
+        self.data = data
+        for key in ("vocab", "width"):
+            if type(data.get(key)) is not int or data[key] < 1:
+                raise ConfigError(f"{key} must be a positive integer, got {data.get(key)!r}")
+        eps = (data.get("norm") or {}).get("eps")
+        if isinstance(eps, bool) or not isinstance(eps, (int, float)) or not eps > 0:
+            raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+        layers = data.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("layers must be a non-empty list")
+        for index, layer in enumerate(layers):
+            kind, mixer = layer.get("type"), layer.get("mixer")
+            if kind not in _MIXER_KEYS:
+                raise ConfigError(f"layers[{index}].type {kind!r} is not one of {sorted(_MIXER_KEYS)}")
+            if not isinstance(mixer, dict) or _MIXER_KEYS[kind] - set(mixer):
+                raise ConfigError(f"layers[{index}].mixer lacks {sorted(_MIXER_KEYS[kind] - set(mixer or {}))}")
+            if kind == "attention":
+                if mixer["heads"] % mixer["kv_heads"]:
+                    raise ConfigError(f"layers[{index}]: {mixer['heads']} heads do not divide into {mixer['kv_heads']} kv heads")
+                source = mixer.get("kv_from")
+                if source is not None:
+                    if type(source) is not int or not 0 <= source < index or layers[source].get("type") != "attention" \
+                            or layers[source]["mixer"].get("kv_from") is not None:
+                        raise ConfigError(f"layers[{index}].mixer.kv_from must name an earlier attention layer with "
+                                          f"keys and values of its own")
+                    theirs = layers[source]["mixer"]
+                    if any(theirs[k] != mixer[k] for k in ("kv_heads", "dim", "vdim")):
+                        raise ConfigError(f"layers[{index}] and layers[{source}] differ in the shape of keys and values")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if mlp.get("kind") == "dense":
+                    if type(mlp.get("ff")) is not int or mlp["ff"] < 1:
+                        raise ConfigError(f"layers[{index}].mlp.ff must be a positive integer")
+                elif mlp.get("kind") == "moe":
+                    router, expert = mlp.get("router") or {}, mlp.get("expert") or {}
+                    if not {"experts", "top"} <= set(router) or not {"ff", "limit"} <= set(expert):
+                        raise ConfigError(f"layers[{index}].mlp needs router.experts, router.top, expert.ff and expert.limit")
+                    if not 1 <= router["top"] <= router["experts"]:
+                        raise ConfigError(f"layers[{index}].mlp: {router['top']} of {router['experts']} experts")
+                    shared = mlp.get("shared")
+                    if shared is not None and not {"ff", "limit"} <= set(shared):
+                        raise ConfigError(f"layers[{index}].mlp.shared needs ff and limit")
+                else:
+                    raise ConfigError(f"layers[{index}].mlp.kind {mlp.get('kind')!r} is neither dense nor moe")
+        self.vocab_size, self.width, self.eps = data["vocab"], data["width"], float(eps)
+        self.layers = layers
+        self.max_positions = int(data.get("max_positions", 1 << 20))
+        eos = data.get("eos_token_id")
+        self.eos_token_ids = frozenset() if eos is None else frozenset(eos if isinstance(eos, list) else [eos])
+
+    @classmethod
+    def from_dict(cls, data: dict) -> "VirulixConfig":
+        if data.get("architecture", cls.architecture) != cls.architecture:
+            raise ConfigError(f"architecture {data.get('architecture')!r} is not {cls.architecture}")
+        return cls(json.loads(json.dumps(data)))
+
+    def to_dict(self) -> dict:
+        return json.loads(json.dumps(self.data)) | {"architecture": self.architecture}
+
+    def __eq__(self, other):
+        return isinstance(other, VirulixConfig) and self.to_dict() == other.to_dict()

@@ -1,7 +1,7 @@
 """The one table from an architecture's name to its configuration class and builder.
 
-``config.json`` names the architecture in ``architectures[0]`` (falling back to
-``model_type``); everything else in the engine asks this table and never a model
+``config.json`` names the architecture in ``architectures[0]`` (or the string
+``architecture``, falling back to ``model_type``); everything else in the engine asks this table and never a model
 class directly.  The reference has no such table: it refuses every ``model_type``
 but ``qwen3`` in place (qil/config.py:37-38).  Adding an architecture is one
 ``register`` call with a configuration class (``from_dict``/``to_dict``) and a
@@ -21,16 +21,19 @@ class Architecture:
     model_type: str
     config_class: type
     build: Callable
+    # True: ``build(config, tensor_shapes=...)`` also takes the shapes of the checkpoint's tensors (name -> shape),
+    # for sizes that a design leaves to the tensors themselves; None when there is no checkpoint
+    shape_aware: bool = False
 
 
 _by_name: dict = {}
 _by_model_type: dict = {}
 
 
-def register(name, model_type, config_class, build) -> Architecture:
+def register(name, model_type, config_class, build, shape_aware=False) -> Architecture:
     if name in _by_name:
         raise ValueError(f"architecture {name} is already registered")
-    entry = Architecture(name, model_type, config_class, build)
+    entry = Architecture(name, model_type, config_class, build, shape_aware)
     _by_name[name] = entry
     _by_model_type.setdefault(model_type, entry)
     return entry
@@ -48,6 +51,8 @@ def known() -> list:
 
 def lookup(config_dict: dict) -> Architecture:
     names = config_dict.get("architectures") or []
+    if not names and isinstance(config_dict.get("architecture"), str):
+        names = [config_dict["architecture"]]          # some designs name themselves in a single string
     if names:
         entry = _by_name.get(names[0])
         if entry is None:

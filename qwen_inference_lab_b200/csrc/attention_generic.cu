@@ -12,6 +12,14 @@
 // Keys are walked in tiles of 128 aligned to absolute positions and summed in
 // ascending order, so a token's result depends only on its own query and the
 // cache contents: not on how the batch was cut or what else is in it.
+//
+// Two options serve other designs than the reference's.  Values may have another
+// size than queries and keys (`v_dim`): a page then holds its key rows
+// [kv_head][slot][head_dim] followed by its value rows [kv_head][slot][v_dim],
+// which for equal sizes is the layout [2][kv_head][slot][head_dim].  And a bias
+// that grows with distance may be taken off the scaled score (`slopes`, one per
+// query head): score = q.k * scale - slope_h * (i - j) for the query at position i
+// and the key at position j.
 #include "common.cuh"
 
 #define GEN_TILE 128
@@ -23,11 +31,12 @@ __global__ void __launch_bounds__(GEN_TILE)
 attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache, T* __restrict__ out,
                          const int* __restrict__ positions, const int* __restrict__ token_row,
                          const int* __restrict__ block_table, int table_stride,
-                         int n_q_heads, int n_kv_heads, int head_dim, int page_size, int num_pages,
-                         int window, float scale) {
+                         int n_q_heads, int n_kv_heads, int head_dim, int v_dim, int page_size, int num_pages,
+                         int window, float scale, const float* __restrict__ slopes) {
     extern __shared__ long long smem_ll[];
     long long* row_off = smem_ll;                      // [GEN_TILE] element offset of each key row, -1 if none
-    float* ks = reinterpret_cast<float*>(row_off + GEN_TILE);  // [GEN_TILE][33]
+    long long* val_off = row_off + GEN_TILE;           // [GEN_TILE] element offset of each value row
+    float* ks = reinterpret_cast<float*>(val_off + GEN_TILE);  // [GEN_TILE][33]
     float* ps = ks + GEN_TILE * 33;                    // [GEN_TILE]
     float* red = ps + GEN_TILE;                        // [32]
     float* qs = red + 32;                              // [head_dim]
@@ -39,6 +48,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int* table = block_table + (size_t)token_row[token] * table_stride;
 
+    const float slope = slopes != nullptr ? slopes[head] : 0.f;
     const T* qrow = q + ((size_t)token * n_q_heads + head) * head_dim;
     for (int d = tid; d < head_dim; d += GEN_TILE) qs[d] = to_f32<T>(qrow[d]);
 
@@ -47,18 +57,23 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
 #pragma unroll
     for (int i = 0; i < GEN_DPT; ++i) acc[i] = 0.f;
 
-    const size_t v_plane = (size_t)n_kv_heads * page_size * head_dim;  // K plane -> V plane of a page
+    const long long page_elems = (long long)n_kv_heads * page_size * (head_dim + v_dim);
+    const long long k_plane = (long long)n_kv_heads * page_size * head_dim;   // a page's key rows come first
     for (int tile = lo / GEN_TILE; tile * GEN_TILE <= pos; ++tile) {
         const int key = tile * GEN_TILE + tid;
         const bool valid = key >= lo && key <= pos;
-        long long off = -1;
+        long long off = -1, voff = -1;
         if (valid) {
             const int page = key / page_size < table_stride ? table[key / page_size] : -1;
-            if (page >= 0 && page < num_pages)
-                off = ((((long long)page * 2) * n_kv_heads + kv_head) * page_size + (key % page_size)) * head_dim;
+            if (page >= 0 && page < num_pages) {
+                const long long row = (long long)kv_head * page_size + (key % page_size);
+                off = page * page_elems + row * head_dim;
+                voff = page * page_elems + k_plane + row * v_dim;
+            }
         }
         __syncthreads();  // previous tile's readers of row_off / ps are done
         row_off[tid] = off;
+        val_off[tid] = voff;
         __syncthreads();
 
         float dot = 0.f;
@@ -73,7 +88,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
             for (int dd = 0; dd < chunk; ++dd) dot = fmaf(qs[d0 + dd], ks[tid * 33 + dd], dot);
             __syncthreads();
         }
-        const float score = (valid && off >= 0) ? dot * scale : -INFINITY;
+        const float score = (valid && off >= 0) ? dot * scale - slope * (float)(pos - key) : -INFINITY;
         const float tile_max = block_max(score, red);
         const float m_new = fmaxf(m_run, tile_max);
         const float p = (score == -INFINITY) ? 0.f : expf(score - m_new);
@@ -85,42 +100,42 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
 #pragma unroll
         for (int i = 0; i < GEN_DPT; ++i) {
             const int d = tid + i * GEN_TILE;
-            if (d < head_dim) {
+            if (d < v_dim) {
                 float a = acc[i] * corr;
                 for (int kk = 0; kk < GEN_TILE; ++kk) {
-                    const long long ro = row_off[kk];
-                    if (ro >= 0) a = fmaf(ps[kk], to_f32<T>(kv_cache[ro + v_plane + d]), a);
+                    const long long vo = val_off[kk];
+                    if (vo >= 0) a = fmaf(ps[kk], to_f32<T>(kv_cache[vo + d]), a);
                 }
                 acc[i] = a;
             }
         }
     }
-    T* orow = out + ((size_t)token * n_q_heads + head) * head_dim;
+    T* orow = out + ((size_t)token * n_q_heads + head) * v_dim;
 #pragma unroll
     for (int i = 0; i < GEN_DPT; ++i) {
         const int d = tid + i * GEN_TILE;
-        if (d < head_dim) orow[d] = from_f32<T>(l_run > 0.f ? acc[i] / l_run : 0.f);
+        if (d < v_dim) orow[d] = from_f32<T>(l_run > 0.f ? acc[i] / l_run : 0.f);
     }
 }
 
 extern "C" int qil_attention_generic(
     const void* q, const void* kv_cache, void* out, const int* positions, const int* token_row,
     const int* block_table, int table_stride, int n_tokens, int n_q_heads, int n_kv_heads,
-    int head_dim, int page_size, int num_pages, int window, float scale, int act_dtype,
-    cudaStream_t stream) {
+    int head_dim, int v_dim, int page_size, int num_pages, int window, float scale, const float* slopes,
+    int act_dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim > GEN_MAX_D)
-        QIL_REFUSE("attention_generic: head_dim %d is outside 1..%d", head_dim, GEN_MAX_D);
+    if (head_dim <= 0 || head_dim > GEN_MAX_D || v_dim <= 0 || v_dim > GEN_MAX_D)
+        QIL_REFUSE("attention_generic: head sizes %d and %d must lie in 1..%d", head_dim, v_dim, GEN_MAX_D);
     if (n_kv_heads <= 0 || n_q_heads <= 0 || n_q_heads % n_kv_heads)
         QIL_REFUSE("attention_generic: %d query heads do not divide into %d kv heads", n_q_heads, n_kv_heads);
     if (n_q_heads > 65535) QIL_REFUSE("attention_generic: too many heads (%d)", n_q_heads);
     if (page_size <= 0 || window < 0) QIL_REFUSE("attention_generic: page_size %d window %d", page_size, window);
     dim3 grid(n_tokens, n_q_heads);
     const size_t smem = (size_t)(head_dim + GEN_TILE * 33 + GEN_TILE + 32) * sizeof(float)
-                        + GEN_TILE * sizeof(long long);
+                        + 2 * GEN_TILE * sizeof(long long);
     QIL_DISPATCH_1(act_dtype,
         (attention_generic_kernel<T><<<grid, GEN_TILE, smem, stream>>>(
             (const T*)q, (const T*)kv_cache, (T*)out, positions, token_row, block_table, table_stride,
-            n_q_heads, n_kv_heads, head_dim, page_size, num_pages, window, scale)));
+            n_q_heads, n_kv_heads, head_dim, v_dim, page_size, num_pages, window, scale, slopes)));
     QIL_CHECK_LAUNCH();
 }

@@ -22,7 +22,8 @@
 // and the accumulators are scaled by rsqrt(mean(x^2) + eps) in the epilogue.  The norm weight rides through the ring as
 // one more stage row.
 //
-// Epilogues: bias, residual (may alias out), float32 output for the LM head,
+// Epilogues: bias, residual (of the output's type; may alias out), float32 output for the LM head
+// or a float32 residual stream,
 // and `silu_pairs`: weight rows stored as groups of [8 gate rows, 8 up rows], for
 // which the block writes silu(gate) * up, 8 values per token
 // (qil/model.py:71; silu(gate) is rounded to bfloat16 before the multiply).
@@ -306,7 +307,9 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         for (int w = 0; w < GSM_WARPS; ++w) v += red[w][r][token];
         v *= inverse_rms(token);
         if (bias != nullptr) v += __bfloat162float(bias[n]);
-        if (residual != nullptr) v = __bfloat162float(residual[(size_t)token * N + n]) + v;
+        if (residual != nullptr)     // the residual has the output's type
+            v = (out_f32 ? reinterpret_cast<const float*>(residual)[(size_t)token * N + n]
+                         : __bfloat162float(residual[(size_t)token * N + n])) + v;
         if (out_f32) reinterpret_cast<float*>(out)[(size_t)token * N + n] = v;
         else reinterpret_cast<bf16*>(out)[(size_t)token * N + n] = __float2bfloat16_rn(v);
     }
@@ -492,7 +495,9 @@ gemm_small_m_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
         for (int w = 0; w < GSM_WARPS; ++w) v += red[w][r][token];
         v *= inverse_rms(token);
         if (bias != nullptr) v += __bfloat162float(bias[n]);
-        if (residual != nullptr) v = __bfloat162float(residual[(size_t)token * N + n]) + v;
+        if (residual != nullptr)     // the residual has the output's type
+            v = (out_f32 ? reinterpret_cast<const float*>(residual)[(size_t)token * N + n]
+                         : __bfloat162float(residual[(size_t)token * N + n])) + v;
         if (out_f32) reinterpret_cast<float*>(out)[(size_t)token * N + n] = v;
         else reinterpret_cast<bf16*>(out)[(size_t)token * N + n] = __float2bfloat16_rn(v);
     }

@@ -1,0 +1,334 @@
+// Mixture of experts: a float32 router with a softmax over the chosen experts, the grouping of
+// (token, chosen expert) pairs by expert, the experts' products over the grouped rows, and the sum of a
+// token's weighted expert outputs onto the residual stream.
+//
+//   route     logits = x R^T + b in float32; the `top` largest (ties: the lower index); weights =
+//             softmax over those logits alone.  One block per token, every dot product by one warp with a
+//             fixed tree: a token's choice never depends on the rest of the batch.
+//   group     pairs p = token * top + slot sorted by expert, and a list of row tiles (expert, first
+//             row, rows) for the products.  One block; no host round trip, so the launch sizes of what
+//             follows depend on the number of tokens only.
+//   gate_up   for every row tile: h = act(A W_gate[e]^T, A W_up[e]^T) with A the tokens' rows gathered
+//             through the pair list; both products share the loads of A; h is written in grouped order.
+//   down      y[p] = weight[p] * (h W_down[e]^T), float32, written at the pair's own place.
+//   combine   out[t] = residual[t] + sum over slots of y[t * top + slot], in slot order.
+//
+// The products run on the CUDA cores with float32 FMA, each output element summing over k in ascending
+// order with one accumulator: a pair's result does not depend on which rows share its tile.
+// The activation is the clamped swish of gated_activation.cu (kind 2) or silu (kind 0).
+#include "common.cuh"
+
+#define MOE_BM 64
+#define MOE_BN 64
+#define MOE_BK 16
+#define MOE_MAX_EXPERTS 1024
+#define MOE_MAX_TOP 64
+
+// ------------------------------------------------------------------ route
+template <typename T, typename W>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W* __restrict__ bias, int width,
+                 int n_experts, int top, int* __restrict__ chosen, float* __restrict__ weights) {
+    __shared__ float logits[MOE_MAX_EXPERTS];
+    __shared__ float sel_p[MOE_MAX_TOP];
+    __shared__ int sel_at[MOE_MAX_TOP];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const size_t token = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* row = x + token * width;
+    for (int e = warp; e < n_experts; e += 4) {
+        const W* w = router + (size_t)e * width;
+        float dot = 0.f;
+        for (int i = lane; i < width; i += 32) dot = fmaf(to_f32<T>(row[i]), to_f32<W>(w[i]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) logits[e] = dot + (bias != nullptr ? to_f32<W>(bias[e]) : 0.f);
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float best_first = 0.f, total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = n_experts;
+        for (int e = lane; e < n_experts; e += 32) {
+            const float v = logits[e];
+            if (v > best) { best = v; at = e; }       // ascending e: the lower index wins a tie inside a lane
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, o);
+            const int other_at = __shfl_xor_sync(0xffffffffu, at, o);
+            if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+        }
+        if (at >= n_experts) { at = k; best = -INFINITY; }      // non-finite logits: still name an expert
+        if (k == 0) best_first = best;
+        const float p = best == -INFINITY ? 0.f : expf(best - best_first);
+        total += p;
+        if (lane == 0) {
+            sel_at[k] = at;
+            sel_p[k] = p;
+            logits[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int k = lane; k < top; k += 32) {
+        chosen[token * top + k] = sel_at[k];
+        weights[token * top + k] = total > 0.f ? sel_p[k] / total : 0.f;
+    }
+}
+
+// ------------------------------------------------------------------ group
+// counts, offsets and the pair list; then the tiles.  info: [0] = number of tiles; tiles: int32 [max_tiles, 3].
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int* __restrict__ sorted_pairs,
+                 int* __restrict__ info, int* __restrict__ tiles, int max_tiles) {
+    __shared__ int counts[MOE_MAX_EXPERTS];
+    __shared__ int cursor[MOE_MAX_EXPERTS];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    for (int e = threadIdx.x; e < n_experts; e += 1024) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += 1024) {
+        const int e = chosen[p];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tile = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            cursor[e] = at;
+            for (int r = 0; r < counts[e] && tile < max_tiles; r += MOE_BM, ++tile) {
+                tiles[3 * tile] = e;
+                tiles[3 * tile + 1] = at + r;
+                tiles[3 * tile + 2] = counts[e] - r < MOE_BM ? counts[e] - r : MOE_BM;
+            }
+            at += counts[e];
+        }
+        info[0] = tile;
+    }
+    __syncthreads();
+    // pairs in ascending order inside every expert: a thread places the pairs of one expert at a time
+    for (int e = threadIdx.x; e < n_experts; e += 1024) {
+        if (counts[e] == 0) continue;
+        int at = cursor[e];
+        for (int p = 0; p < n_pairs; ++p)
+            if (chosen[p] == e) sorted_pairs[at++] = p;
+    }
+}
+
+// The same grouping for many pairs: placement by atomic cursor (the order inside an expert then
+// varies from run to run, the results do not: every row of a product is computed by itself).
+__global__ void __launch_bounds__(1024)
+moe_place_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int* __restrict__ cursor_global,
+                 int* __restrict__ sorted_pairs) {
+    for (int p = blockIdx.x * 1024 + threadIdx.x; p < n_pairs; p += gridDim.x * 1024) {
+        const int e = chosen[p];
+        if (e >= 0 && e < n_experts) sorted_pairs[atomicAdd(&cursor_global[e], 1)] = p;
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+moe_count_kernel(const int* __restrict__ chosen, int n_pairs, int n_experts, int* __restrict__ cursor_global,
+                 int* __restrict__ info, int* __restrict__ tiles, int max_tiles) {
+    __shared__ int counts[MOE_MAX_EXPERTS];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    for (int e = threadIdx.x; e < n_experts; e += 1024) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += 1024) {
+        const int e = chosen[p];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tile = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            cursor_global[e] = at;
+            for (int r = 0; r < counts[e] && tile < max_tiles; r += MOE_BM, ++tile) {
+                tiles[3 * tile] = e;
+                tiles[3 * tile + 1] = at + r;
+                tiles[3 * tile + 2] = counts[e] - r < MOE_BM ? counts[e] - r : MOE_BM;
+            }
+            at += counts[e];
+        }
+        info[0] = tile;
+    }
+}
+
+// ------------------------------------------------------------------ the experts' products
+__device__ __forceinline__ float expert_activation(int kind, float g, float u, float limit, float alpha) {
+    if (kind == 0) return g / (1.f + expf(-g)) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+}
+
+// DUAL: two weight stacks (gate, up) [experts, n_out, k]; rows of A gathered by pair / top; activation; output
+// in grouped order.  Otherwise one stack; rows of A in grouped order; output float32 at the pair's place, scaled.
+template <typename T, typename W, bool DUAL>
+__global__ void __launch_bounds__(256)
+moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w0, const W* __restrict__ w1,
+                       const int* __restrict__ tiles, const int* __restrict__ info,
+                       const int* __restrict__ sorted_pairs, int top, const float* __restrict__ pair_weight,
+                       T* __restrict__ hidden, float* __restrict__ y, int n_out, int K, int kind, float limit,
+                       float alpha) {
+    __shared__ float As[MOE_BK][MOE_BM + 4];
+    __shared__ float W0s[MOE_BK][MOE_BN + 4];
+    __shared__ float W1s[DUAL ? MOE_BK : 1][MOE_BN + 4];
+    __shared__ int src_row[MOE_BM];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const int tile = blockIdx.y;
+    if (tile >= info[0]) return;
+    const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int n0 = blockIdx.x * MOE_BN;
+    if (tid < MOE_BM) src_row[tid] = tid < rows ? (DUAL ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
+    __syncthreads();
+    const W* e0 = w0 + (size_t)expert * n_out * K;
+    const W* e1 = DUAL ? w1 + (size_t)expert * n_out * K : nullptr;
+    float acc0[4][4], acc1[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc0[i][j] = acc1[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += MOE_BK) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * 256;
+            const int r = idx >> 4, kk = idx & 15, k = k0 + kk;
+            float a = 0.f, b0 = 0.f, b1 = 0.f;
+            if (k < K) {
+                if (src_row[r] >= 0) a = to_f32<T>(A[(size_t)src_row[r] * lda + k]);
+                if (n0 + r < n_out) {
+                    b0 = to_f32<W>(e0[(size_t)(n0 + r) * K + k]);
+                    if (DUAL) b1 = to_f32<W>(e1[(size_t)(n0 + r) * K + k]);
+                }
+            }
+            As[kk][r] = a;
+            W0s[kk][r] = b0;
+            if (DUAL) W1s[kk][r] = b1;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MOE_BK; ++kk) {
+            float a[4], b0[4], b1[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { b0[j] = W0s[kk][tx * 4 + j]; b1[j] = DUAL ? W1s[kk][tx * 4 + j] : 0.f; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    acc0[i][j] = fmaf(a[i], b0[j], acc0[i][j]);
+                    if (DUAL) acc1[i][j] = fmaf(a[i], b1[j], acc1[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+        const int pair = DUAL ? 0 : sorted_pairs[row0 + r];
+        const float scale = DUAL ? 1.f : pair_weight[pair];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= n_out) continue;
+            if (DUAL) {
+                // the products are rounded to the activation type first, as a projection's output is
+                const float g = round_to<T>(acc0[i][j]), u = round_to<T>(acc1[i][j]);
+                hidden[(size_t)(row0 + r) * n_out + n] = from_f32<T>(expert_activation(kind, g, u, limit, alpha));
+            } else {
+                y[(size_t)pair * n_out + n] = scale * acc0[i][j];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ combine
+template <typename R>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ y, const R* __restrict__ residual, R* __restrict__ out, size_t total,
+                   int width, int top) {
+    qil_wait_for_producer();
+    qil_release_consumer();
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
+        const size_t token = i / width;
+        const int col = (int)(i % width);
+        float sum = 0.f;
+        for (int s = 0; s < top; ++s) sum += y[(token * top + s) * width + col];
+        out[i] = from_f32<R>(residual != nullptr ? to_f32<R>(residual[i]) + sum : sum);
+    }
+}
+
+// ------------------------------------------------------------------ entry points
+extern "C" int qil_moe_route(const void* x, const void* router, const void* bias, int n_tokens, int width,
+                             int n_experts, int top, int* chosen, float* weights, int act_dtype, int weight_dtype,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_experts <= 0 || n_experts > MOE_MAX_EXPERTS || top <= 0 || top > n_experts || top > MOE_MAX_TOP || width <= 0)
+        QIL_REFUSE("moe_route: %d experts (at most %d), %d of them per token, width %d", n_experts, MOE_MAX_EXPERTS, top, width);
+    QIL_DISPATCH_2(act_dtype, weight_dtype,
+        qil_launch_chained(moe_route_kernel<T, W>, dim3(n_tokens), dim3(128), 0, stream, (const T*)x, (const W*)router,
+                           (const W*)bias, width, n_experts, top, chosen, weights));
+    QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_moe_tile_rows() { return MOE_BM; }
+
+// work: int32 [1 + n_experts] (tile count, then a cursor per expert); tiles: int32 [max_tiles, 3].
+extern "C" int qil_moe_group(const int* chosen, int n_pairs, int n_experts, int* sorted_pairs, int* work, int* tiles,
+                             int max_tiles, cudaStream_t stream) {
+    if (n_pairs <= 0) return 0;
+    if (n_experts <= 0 || n_experts > MOE_MAX_EXPERTS) QIL_REFUSE("moe_group: %d experts", n_experts);
+    if (n_pairs <= 4096) {
+        qil_launch_chained(moe_group_kernel, dim3(1), dim3(1024), 0, stream, chosen, n_pairs, n_experts, sorted_pairs,
+                           work, tiles, max_tiles);
+    } else {
+        qil_launch_chained(moe_count_kernel, dim3(1), dim3(1024), 0, stream, chosen, n_pairs, n_experts, work + 1, work,
+                           tiles, max_tiles);
+        const int blocks = (n_pairs + 1023) / 1024 < 296 ? (n_pairs + 1023) / 1024 : 296;
+        moe_place_kernel<<<blocks, 1024, 0, stream>>>(chosen, n_pairs, n_experts, work + 1, sorted_pairs);
+    }
+    QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_moe_gate_up(const void* x, int lda, const void* gate_w, const void* up_w, const int* tiles,
+                               const int* info, int max_tiles, const int* sorted_pairs, int top, void* hidden,
+                               int n_out, int K, int kind, float limit, float alpha, int act_dtype, int weight_dtype,
+                               cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    if (max_tiles > 65535) QIL_REFUSE("moe_gate_up: %d row tiles are too many for one launch", max_tiles);
+    dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
+    QIL_DISPATCH_2(act_dtype, weight_dtype,
+        (qil_launch_chained(moe_expert_gemm_kernel<T, W, true>, grid, dim3(256), 0, stream, (const T*)x, lda,
+                            (const W*)gate_w, (const W*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
+                            (T*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha)));
+    QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_moe_down(const void* hidden, const void* down_w, const int* tiles, const int* info, int max_tiles,
+                            const int* sorted_pairs, const float* pair_weight, float* y, int n_out, int K,
+                            int act_dtype, int weight_dtype, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    if (max_tiles > 65535) QIL_REFUSE("moe_down: %d row tiles are too many for one launch", max_tiles);
+    dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
+    QIL_DISPATCH_2(act_dtype, weight_dtype,
+        (qil_launch_chained(moe_expert_gemm_kernel<T, W, false>, grid, dim3(256), 0, stream, (const T*)hidden, K,
+                            (const W*)down_w, (const W*)nullptr, tiles, info, sorted_pairs, 1, pair_weight,
+                            (T*)nullptr, y, n_out, K, 0, 0.f, 0.f)));
+    QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_moe_combine(const float* y, const void* residual, void* out, int n_tokens, int width, int top,
+                               int stream_dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const size_t total = (size_t)n_tokens * width;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    QIL_DISPATCH_1(stream_dtype,
+        qil_launch_chained(moe_combine_kernel<T>, dim3(blocks), dim3(256), 0, stream, y, (const T*)residual, (T*)out,
+                           total, width, top));
+    QIL_CHECK_LAUNCH();
+}

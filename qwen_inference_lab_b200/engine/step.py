@@ -213,7 +213,8 @@ class StepRunner:
             seg_pos0=section("seg_pos0"), plans=plans,
             max_context=description.max_context if max_context is None else max_context, min_context=min_context,
             h_seg_row=segments.rows, h_seg_start=segments.first, h_seg_len=segments.lens,
-            h_seg_pos0=segments.starts, extras=self._extras)
+            h_seg_pos0=segments.starts, extras=self._extras,
+            stream_dtype=getattr(self.model, "stream_dtype", None))
 
     def _upload(self, packed):
         self._reserve(len(packed))

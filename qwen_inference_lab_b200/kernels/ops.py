@@ -17,7 +17,7 @@ F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "gemm_small_m.cu", "attention_generic.cu",
-                "sampling.cu"]
+                "sampling.cu", "norm_exact.cu", "gated_activation.cu", "qkv_store.cu", "gla_scan.cu", "moe.cu"]
 SMALL_M_MAX_ROWS = min(16, tuning.SMALL_M_MAX_ROWS)      # the kernel takes 16 at most
 
 _core = None
@@ -232,7 +232,7 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
     if bias is not None:
         _need(bias, "bias", torch.bfloat16, 1)
     if residual is not None:
-        _need(residual, "residual", torch.bfloat16, 2)
+        _need(residual, "residual", out_dtype, 2)          # a float32 output adds a float32 residual
         if residual.shape != out_shape:
             raise KernelError("gemm_small_m: residual has the wrong shape")
     if out is None:
@@ -363,23 +363,215 @@ def qk_norm_rope_store(qkv, q_out, kv_cache, q_norm_w, k_norm_w, eps, rope_table
     return q_out
 
 
+def check_pages(kv_cache, dtype, n_kv_heads, page_size, head_dim, v_dim, what):
+    """One layer's pages: [pages, 2, kv_heads, page_size, head_dim] when keys and values have one size,
+    else [pages, kv_heads * page_size * (head_dim + v_dim)] (a page's key rows, then its value rows)."""
+    _need(kv_cache, "kv_cache", dtype)
+    equal = tuple(kv_cache.shape[1:]) == (2, n_kv_heads, page_size, head_dim) and v_dim == head_dim
+    flat = kv_cache.ndim == 2 and kv_cache.shape[1] == n_kv_heads * page_size * (head_dim + v_dim)
+    if not (equal or flat):
+        raise KernelError(f"{what}: cache layout {tuple(kv_cache.shape)} for {n_kv_heads} heads of {head_dim}/{v_dim}, "
+                          f"pages of {page_size}")
+
+
 def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_heads, n_kv_heads,
-                      head_dim, page_size, window, scale):
-    """Causal GQA attention of every token over its request's pages (CUDA cores, float32 math)."""
-    _need(q, "q", ndim=2); _need(out, "out", q.dtype, 2); _need(kv_cache, "kv_cache", q.dtype, 5)
+                      head_dim, page_size, window, scale, v_dim=None, slopes=None):
+    """Causal GQA attention of every token over its request's pages (CUDA cores, float32 math).
+
+    ``v_dim``: the size of a value head when it differs from ``head_dim`` (out is then [N, Hq * v_dim]).
+    ``slopes`` float32 [Hq]: score = q.k * scale - slopes[h] * (query position - key position)."""
+    v_dim = head_dim if v_dim is None else int(v_dim)
+    _need(q, "q", ndim=2); _need(out, "out", q.dtype, 2)
+    check_pages(kv_cache, q.dtype, n_kv_heads, page_size, head_dim, v_dim, "attention_generic")
     n = q.shape[0]
-    if q.shape[1] != n_q_heads * head_dim or out.shape != q.shape:
+    if q.shape[1] != n_q_heads * head_dim or out.shape != (n, n_q_heads * v_dim):
         raise KernelError("attention_generic: q/out shapes do not match the head counts")
-    if tuple(kv_cache.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
-        raise KernelError(f"attention_generic: cache layout {tuple(kv_cache.shape)}")
+    if slopes is not None:
+        _need(slopes, "slopes", torch.float32, 1)
+        if slopes.shape[0] != n_q_heads:
+            raise KernelError("attention_generic: one slope per query head")
     _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
     _need(block_table, "block_table", torch.int32, 2)
     lib = core()
     _check(lib, lib.qil_attention_generic(
         _p(q), _p(kv_cache), _p(out), _p(positions), _p(token_row), _p(block_table), c_int(block_table.shape[1]),
-        c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
-        c_int(kv_cache.shape[0]), c_int(window), c_float(scale), c_int(dtype_code(q.dtype)), _stream()),
+        c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_dim), c_int(page_size),
+        c_int(kv_cache.shape[0]), c_int(window), c_float(scale), _p(slopes), c_int(dtype_code(q.dtype)), _stream()),
         "attention_generic")
+    return out
+
+
+def rmsnorm_exact(x, weight, eps, offset=0.0, out_dtype=None, rows=None, out=None):
+    """y = x / sqrt(mean(x^2) + eps) * (offset + weight) with float32 arithmetic and one rounding.
+    ``x`` float32 or bfloat16 [N, width]; the result has ``out_dtype`` (default: x's)."""
+    _need(x, "x", ndim=2); _need(weight, "weight", ndim=1)
+    width = x.shape[1]
+    if weight.shape[0] != width:
+        raise KernelError(f"rmsnorm_exact: weight of {weight.shape[0]} for width {width}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    n_rows = x.shape[0] if rows is None else rows.shape[0]
+    if out is None:
+        out = torch.empty((n_rows, width), dtype=out_dtype or x.dtype, device=x.device)
+    _need(out, "out", ndim=2)
+    if out.shape != (n_rows, width):
+        raise KernelError("rmsnorm_exact: out has the wrong shape")
+    lib = core()
+    _check(lib, lib.qil_rmsnorm_exact(_p(x), c_int(dtype_code(x.dtype)), _p(weight), c_int(dtype_code(weight.dtype)),
+                                      _p(rows), _p(out), c_int(dtype_code(out.dtype)), c_int(n_rows), c_int(width),
+                                      c_float(eps), c_float(offset), _stream()), "rmsnorm_exact")
+    return out
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def gated_activation(gate_up, kind, *, limit=0.0, alpha=1.0, pairs8=False, out=None):
+    """out = act(gate) * f(up) for rows of [gate columns, up columns]: ``kind`` is ``silu``, ``gelu_tanh``, or
+    ``clamped_swish``: min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1)."""
+    _need(gate_up, "gate_up", ndim=2)
+    if gate_up.shape[1] % 2:
+        raise KernelError("gated_activation: the input's width must be even (gate columns then up columns)")
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"gated_activation: unknown kind {kind!r} (known: {sorted(ACTIVATIONS)})")
+    width = gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((gate_up.shape[0], width), dtype=gate_up.dtype, device=gate_up.device)
+    _need(out, "out", gate_up.dtype, 2)
+    lib = core()
+    _check(lib, lib.qil_gated_activation(_p(gate_up), _p(out), c_int(gate_up.shape[0]), c_int(width),
+                                         c_int(dtype_code(gate_up.dtype)), c_int(1 if pairs8 else 0),
+                                         c_int(ACTIVATIONS[kind]), c_float(limit), c_float(alpha), _stream()),
+           "gated_activation")
+    return out
+
+
+def qkv_store(qkv, q_out, kv_cache, positions, token_row, block_table, n_q_heads, n_kv_heads, head_dim, v_dim,
+              page_size, temp_coef=0.0, temp_every=0):
+    """Copy the queries of ``qkv`` [N, Hq*d + Hkv*d + Hkv*e] to ``q_out`` (times 1 + coef * ln(floor((p + 1) /
+    every) + 1) at position p when ``temp_coef`` is set) and write keys and values into the pages.
+    With n_kv_heads == 0 ``qkv`` holds queries only."""
+    _need(qkv, "qkv", ndim=2); _need(q_out, "q_out", qkv.dtype, 2)
+    n = qkv.shape[0]
+    if qkv.shape[1] != n_q_heads * head_dim + n_kv_heads * (head_dim + v_dim) or q_out.shape != (n, n_q_heads * head_dim):
+        raise KernelError("qkv_store: qkv/q_out shapes do not match the head counts")
+    _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
+    num_pages = 0
+    if n_kv_heads:
+        check_pages(kv_cache, qkv.dtype, n_kv_heads, page_size, head_dim, v_dim, "qkv_store")
+        _need(block_table, "block_table", torch.int32, 2)
+        num_pages = kv_cache.shape[0]
+    lib = core()
+    _check(lib, lib.qil_qkv_store(
+        _p(qkv), _p(q_out), _p(kv_cache if n_kv_heads else None), _p(positions), _p(token_row),
+        _p(block_table if n_kv_heads else None), c_int(block_table.shape[1] if n_kv_heads else 0), c_int(n),
+        c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_dim), c_int(page_size), c_int(num_pages),
+        c_float(temp_coef), c_int(temp_every), c_int(dtype_code(qkv.dtype)), _stream()), "qkv_store")
+    return q_out
+
+
+def gla_scan_needs_scratch(d, e) -> bool:
+    code = core().qil_gla_scan_needs_scratch(c_int(d), c_int(e))
+    if code < 0:
+        raise KernelError(f"gla_scan: {d} key channels per head are too many")
+    return bool(code)
+
+
+def gla_scan(projected, columns, a2, a2_bias, tau, q_scale, norm_weight, eps, state, seg_start, seg_len, seg_row,
+             n_segments, n_heads, d, e, out, scratch=None):
+    """Gated linear attention over the segments of a step (see csrc/gla_scan.cu for the equations).
+
+    ``projected`` [N, width]: the stacked projection; ``columns`` = (q, k, v, g, low) first columns in it
+    (q, k: n_heads * d wide; v, g: n_heads * e; low: a2.shape[1]).  ``state`` float32 [slots, n_heads, d, e]
+    is read and written at the rows ``seg_row`` names.  ``out`` [N, n_heads * e]."""
+    _need(projected, "projected", ndim=2); _need(out, "out", projected.dtype, 2)
+    _need(a2, "a2", ndim=2); _need(a2_bias, "a2_bias", a2.dtype, 1); _need(norm_weight, "norm_weight", a2.dtype, 1)
+    _need(state, "state", torch.float32, 4)
+    n, ld = projected.shape
+    rank = a2.shape[1]
+    q_at, k_at, v_at, g_at, low_at = (int(c) for c in columns)
+    if (a2.shape[0] != n_heads * d or a2_bias.shape[0] != n_heads * d or norm_weight.shape[0] != e
+            or tuple(state.shape[1:]) != (n_heads, d, e) or out.shape != (n, n_heads * e)):
+        raise KernelError("gla_scan: shapes do not match the head counts")
+    if max(q_at + n_heads * d, k_at + n_heads * d, v_at + n_heads * e, g_at + n_heads * e, low_at + rank) > ld:
+        raise KernelError("gla_scan: a column range lies outside the projection")
+    for t in (seg_start, seg_len, seg_row):
+        _need(t, "segments", torch.int32, 1)
+    if scratch is not None:
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < n * n_heads * e:
+            raise KernelError("gla_scan: the scratch buffer is too small")
+    size = projected.element_size()
+    base = projected.data_ptr()
+    lib = core()
+    _check(lib, lib.qil_gla_scan(
+        c_void_p(base + q_at * size), c_void_p(base + k_at * size), c_void_p(base + v_at * size),
+        c_void_p(base + g_at * size), c_void_p(base + low_at * size), c_int(ld), _p(a2), _p(a2_bias), c_int(rank),
+        c_float(tau), c_float(q_scale), _p(norm_weight), c_float(eps), _p(state), _p(seg_start), _p(seg_len),
+        _p(seg_row), c_int(n_segments), c_int(n), c_int(n_heads), c_int(d), c_int(e), _p(scratch), _p(out),
+        c_int(dtype_code(projected.dtype)), c_int(dtype_code(a2.dtype)), _stream()), "gla_scan",
+        kernels=1 if scratch is None else 2)
+    return out
+
+
+def moe_route(x, router, bias, top):
+    """(chosen int32 [N, top], weights float32 [N, top]): the ``top`` largest of x R^T + b per row (float32
+    arithmetic; the lower index wins a tie) and the softmax over those logits alone."""
+    _need(x, "x", ndim=2); _need(router, "router", ndim=2)
+    if router.shape[1] != x.shape[1]:
+        raise KernelError("moe_route: the router's width differs from x's")
+    if bias is not None:
+        _need(bias, "bias", router.dtype, 1)
+    n = x.shape[0]
+    chosen = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    lib = core()
+    _check(lib, lib.qil_moe_route(_p(x), _p(router), _p(bias), c_int(n), c_int(x.shape[1]), c_int(router.shape[0]),
+                                  c_int(top), _p(chosen), _p(weights), c_int(dtype_code(x.dtype)),
+                                  c_int(dtype_code(router.dtype)), _stream()), "moe_route")
+    return chosen, weights
+
+
+def moe_experts(x, chosen, weights, gate_w, up_w, down_w, kind, *, limit=0.0, alpha=1.0, residual=None, out=None):
+    """out = residual + sum over a token's chosen experts of weight * down_e(act(gate_e x, up_e x)).
+
+    gate_w, up_w [E, ff, width]; down_w [E, width, ff]; ``kind`` as in ``gated_activation`` (``silu`` or
+    ``clamped_swish``).  ``residual`` and ``out`` [N, width] share a dtype (the residual stream's)."""
+    _need(x, "x", ndim=2); _need(chosen, "chosen", torch.int32, 2); _need(weights, "weights", torch.float32, 2)
+    _need(gate_w, "gate_w", ndim=3); _need(up_w, "up_w", gate_w.dtype, 3); _need(down_w, "down_w", gate_w.dtype, 3)
+    n, width = x.shape
+    experts, ff, _ = gate_w.shape
+    top = chosen.shape[1]
+    if (gate_w.shape != (experts, ff, width) or up_w.shape != gate_w.shape or down_w.shape != (experts, width, ff)
+            or chosen.shape[0] != n or weights.shape != chosen.shape):
+        raise KernelError("moe_experts: shapes do not fit together")
+    if kind not in ("silu", "clamped_swish"):
+        raise KernelError(f"moe_experts: activation {kind!r}")
+    stream_dtype = residual.dtype if residual is not None else (out.dtype if out is not None else x.dtype)
+    if out is None:
+        out = torch.empty((n, width), dtype=stream_dtype, device=x.device)
+    _need(out, "out", stream_dtype, 2)
+    if residual is not None:
+        _need(residual, "residual", stream_dtype, 2)
+    lib = core()
+    pairs = n * top
+    tile_rows = lib.qil_moe_tile_rows()
+    max_tiles = min(pairs, pairs // tile_rows + experts)
+    work = torch.empty(1 + experts + pairs + 3 * max_tiles, dtype=torch.int32, device=x.device)
+    info, sorted_pairs, tiles = work[:1 + experts], work[1 + experts:1 + experts + pairs], work[1 + experts + pairs:]
+    hidden = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+    y = torch.empty((pairs, width), dtype=torch.float32, device=x.device)
+    act, wt = c_int(dtype_code(x.dtype)), c_int(dtype_code(gate_w.dtype))
+    _check(lib, lib.qil_moe_group(_p(chosen), c_int(pairs), c_int(experts), _p(sorted_pairs), _p(info), _p(tiles),
+                                  c_int(max_tiles), _stream()), "moe_group", kernels=1 if pairs <= 4096 else 2)
+    _check(lib, lib.qil_moe_gate_up(_p(x), c_int(width), _p(gate_w), _p(up_w), _p(tiles), _p(info), c_int(max_tiles),
+                                    _p(sorted_pairs), c_int(top), _p(hidden), c_int(ff), c_int(width),
+                                    c_int(ACTIVATIONS[kind]), c_float(limit), c_float(alpha), act, wt, _stream()),
+           "moe_gate_up")
+    _check(lib, lib.qil_moe_down(_p(hidden), _p(down_w), _p(tiles), _p(info), c_int(max_tiles), _p(sorted_pairs),
+                                 _p(weights), _p(y), c_int(width), c_int(ff), act, wt, _stream()), "moe_down")
+    _check(lib, lib.qil_moe_combine(_p(y), _p(residual), _p(out), c_int(n), c_int(width), c_int(top),
+                                    c_int(dtype_code(stream_dtype)), _stream()), "moe_combine")
     return out
 
 

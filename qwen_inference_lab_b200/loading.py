@@ -40,9 +40,21 @@ def load_model(directory, *, device="cuda", dtype=torch.bfloat16, keep_stored_32
     are instead of casting them (``weights.loader``)."""
     device, dtype = require_gpu(device), resolve_dtype(dtype)
     entry, config = registry.read_model_config(directory)
-    model = entry.build(config)
+    model = entry.build(config, tensor_shapes=tensor_shapes(directory)) if entry.shape_aware else entry.build(config)
     load_weights(model, directory, device=device, dtype=dtype, keep_stored_32bit=keep_stored_32bit)
     return model
+
+
+def tensor_shapes(directory) -> dict:
+    """Tensor name -> shape over the folder's safetensors files (headers only)."""
+    from pathlib import Path
+    from .weights import SafetensorsFile
+    shapes = {}
+    for path in sorted(Path(directory).glob("*.safetensors")):
+        with SafetensorsFile(path) as shard:
+            for name in shard.keys():
+                shapes[name] = tuple(shard.shape(name))
+    return shapes
 
 
 def random_model(config, seed=0, *, device="cuda", dtype=torch.bfloat16):

@@ -1,2 +1,3 @@
 """Importing this package registers every architecture the engine knows."""
 from . import qwen3  # noqa: F401
+from . import virulix  # noqa: F401

@@ -2,9 +2,11 @@
 from .base import (FeedForward, KVCacheSpec, Mixer, Norm, Param, Part, PlanView, PositionEncoding, Segments,
                    StateSpec, StepContext, StepPlanner)
 from .linear import Linear, StackedLinear
-from .norm import RMSNorm
+from .norm import ExactRMSNorm, RMSNorm
 from .rotary import RotaryEmbedding, rotary_table
 from .attention import GroupedQueryAttention
 from .feed_forward import GatedMLP
+from .experts import RoutedExperts
+from .linear_attention import GatedLinearAttention
 from .block import PreNormBlock
 from .decoder import DecoderModel, LayerCall, TokenEmbedding

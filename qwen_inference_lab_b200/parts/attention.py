@@ -7,6 +7,12 @@ token's own position (inside the window, if one is set), times v, then the outpu
 projection (qil/model.py:48-69 for a chunk, :73-84 for single tokens; both are
 the same computation here, every token of the flat batch takes it).  Query head
 ``h`` reads kv head ``h // (n_q_heads // n_kv_heads)`` (qil/paged_attention.py:21).
+
+Options for designs without rotation: a bias that grows with distance taken off the scaled score
+(``distance_slopes``, one slope per query head: score = q.k * scale - slope_h * (i - j)), a query
+temperature that grows with the logarithm of the position (``q_temperature`` = (coef, every):
+q_p * (1 + coef * ln(floor((p + 1) / every) + 1))), and value heads of another size than key heads
+(``v_head_dim``).
 """
 from __future__ import annotations
 
@@ -45,7 +51,9 @@ class GroupedQueryAttention(Mixer):
     graph_safe = True
 
     def __init__(self, hidden_size, n_q_heads, n_kv_heads, head_dim, *, names, bias=False,
-                 qk_norm_eps=None, position=None, window=0, scale=None, reads_shared_cache=False):
+                 qk_norm_eps=None, position=None, window=0, scale=None, reads_shared_cache=False,
+                 v_head_dim=None, distance_slopes=None, q_temperature=None, out_bias=None,
+                 suffixes=(".weight", ".bias")):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads do not divide into {n_kv_heads} kv heads")
         self.hidden_size, self.head_dim = int(hidden_size), int(head_dim)
@@ -55,11 +63,25 @@ class GroupedQueryAttention(Mixer):
         self.qk_norm_eps = qk_norm_eps
         self.position = position
         self.reads_shared_cache = bool(reads_shared_cache)
+        self.v_head_dim = int(v_head_dim) if v_head_dim else self.head_dim
+        self.distance_slopes = None if distance_slopes is None else [float(v) for v in distance_slopes]
+        if self.distance_slopes is not None and len(self.distance_slopes) != self.n_q_heads:
+            raise ValueError("distance_slopes needs one slope per query head")
+        self.q_temperature = None if not q_temperature else (float(q_temperature[0]), int(q_temperature[1]))
+        if self.q_temperature is not None and self.q_temperature[1] < 1:
+            raise ValueError("the query temperature's step must be a positive number of positions")
+        # without per-head norms and rotation the projection's tail is a copy (times the temperature) and the page write
+        self.plain_tail = (self.v_head_dim != self.head_dim or self.distance_slopes is not None
+                           or self.q_temperature is not None)
+        if self.plain_tail and (qk_norm_eps is not None or position is not None):
+            raise ValueError("distance slopes, query temperature and a value size of its own go without q/k norms and rotation")
+        self._slopes = None
         pieces = [(names["q"], n_q_heads * head_dim)]
         if not self.reads_shared_cache:
-            pieces += [(names["k"], n_kv_heads * head_dim), (names["v"], n_kv_heads * head_dim)]
-        self.qkv = StackedLinear(hidden_size, pieces, bias=bias)
-        self.out = Linear(n_q_heads * head_dim, hidden_size, name=names["o"], bias=bias)
+            pieces += [(names["k"], n_kv_heads * head_dim), (names["v"], n_kv_heads * self.v_head_dim)]
+        self.qkv = StackedLinear(hidden_size, pieces, bias=bias, suffixes=suffixes)
+        self.out = Linear(n_q_heads * self.v_head_dim, hidden_size, name=names["o"],
+                          bias=bias if out_bias is None else out_bias, suffixes=suffixes)
         self.q_norm = self.k_norm = None
         self._norm_names = None
         if qk_norm_eps is not None:
@@ -82,6 +104,8 @@ class GroupedQueryAttention(Mixer):
         super().finalize(device, dtype)
         if self.q_norm is not None and self.q_norm.data.dtype != self.k_norm.data.dtype:
             self.q_norm.data, self.k_norm.data = self.q_norm.data.float(), self.k_norm.data.float()
+        if self.distance_slopes is not None:
+            self._slopes = torch.tensor(self.distance_slopes, dtype=torch.float32, device=device)
 
     def step_planners(self):
         return {**super().step_planners(), _PLANNER.key: _PLANNER}
@@ -89,7 +113,8 @@ class GroupedQueryAttention(Mixer):
     def cache_spec(self):
         if self.reads_shared_cache:
             return None
-        return KVCacheSpec(self.n_kv_heads, self.head_dim, self.window)
+        return KVCacheSpec(self.n_kv_heads, self.head_dim, self.window,
+                           self.v_head_dim if self.v_head_dim != self.head_dim else 0)
 
     takes_norm = True
 
@@ -98,6 +123,15 @@ class GroupedQueryAttention(Mixer):
         the block's un-normed input and the first projection applies the norm."""
         n = x.shape[0]
         n_kv = 0 if self.reads_shared_cache else self.n_kv_heads
+        if self.plain_tail:
+            qkv = self.qkv.forward(ctx, x, norm=norm)
+            q = ctx.empty((n, self.n_q_heads * self.head_dim))
+            coef, every = self.q_temperature or (0.0, 0)
+            ops.qkv_store(qkv, q, cache.pages, ctx.positions, ctx.token_row, cache.block_table, self.n_q_heads, n_kv,
+                          self.head_dim, self.v_head_dim, cache.page_size, coef, every)
+            attended = ctx.empty((n, self.n_q_heads * self.v_head_dim))
+            self._attend(ctx, q, cache, attended)
+            return self.out.forward(ctx, attended, residual=residual)
         table = self.position.table if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         q_norm = self.q_norm.data if self.q_norm is not None else None
@@ -131,10 +165,11 @@ class GroupedQueryAttention(Mixer):
         return self.out.forward(ctx, attended, residual=residual)
 
     def _attend(self, ctx, q, cache, out):
-        if q.dtype == torch.bfloat16 and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads):
+        if not self.plain_tail and q.dtype == torch.bfloat16 \
+                and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads):
             attention_mma.attend(ctx, q, cache, out, self.n_q_heads, self.n_kv_heads, self.head_dim,
                                  self.window, self.scale)
             return
         ops.attention_generic(q, cache.pages, out, ctx.positions, ctx.token_row, cache.block_table,
                               self.n_q_heads, self.n_kv_heads, self.head_dim, cache.page_size,
-                              self.window, self.scale)
+                              self.window, self.scale, v_dim=self.v_head_dim, slopes=self._slopes)

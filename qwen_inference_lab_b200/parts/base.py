@@ -39,11 +39,14 @@ class Param:
     ``keep_32bit``: a tensor that the checkpoint stores in 32 bits stays so in a bfloat16 run (for
     parameters whose part computes in float32, such as router weights or decay rates); all others
     are cast to the run's dtype when they are loaded, as the reference does (qil/model.py:197).
+    ``optional``: a tensor that a checkpoint may leave out (the loader then leaves ``data`` None and the
+    part that owns it must not use it).
     """
 
-    __slots__ = ("shape", "init", "std", "data", "integer", "keep_32bit")
+    __slots__ = ("shape", "init", "std", "data", "integer", "keep_32bit", "optional")
 
-    def __init__(self, shape, init="normal", std=0.02, integer=False, keep_32bit=False):
+    def __init__(self, shape, init="normal", std=0.02, integer=False, keep_32bit=False, optional=False):
+        self.optional = optional
         self.shape = tuple(int(n) for n in shape)
         self.init = init
         self.std = std
@@ -61,10 +64,16 @@ class KVCacheSpec:
 
     ``window`` > 0 means that only the last ``window`` positions are ever read, so
     pages that the window has passed are given back while the request lives.
+    ``v_head_dim``: the size of a value head where it differs from a key head's (0: the same).
     """
     kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
 
 
 @dataclass(frozen=True)
@@ -224,6 +233,8 @@ class StepContext:
     h_seg_pos0: object = None
     # the runner's own dict, the same one every step: parts keep scratch buffers here under their own keys
     extras: dict = field(default_factory=dict)
+    # dtype of the residual stream when it differs from the activations' (a model that keeps it in float32)
+    stream_dtype: torch.dtype | None = None
 
     def empty(self, shape, dtype=None):
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)

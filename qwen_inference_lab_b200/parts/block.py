@@ -3,7 +3,8 @@
 The pre-norm order of the reference's ``DecoderBlock.forward`` (qil/model.py:48-71).
 The block owns no sizes: it is given a norm, a mixer, a second norm and a
 feed-forward, each already built, so different layers of one model may hold
-different kinds of each.
+different kinds of each.  ``feed_forward`` may be None: the layer is then its mixer
+alone (a second norm given all the same only claims its tensor).
 """
 from __future__ import annotations
 
@@ -17,7 +18,7 @@ class PreNormBlock(Part):
         self.graph_safe = True
 
     def children(self):
-        return [self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward]
+        return [part for part in (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward) if part is not None]
 
     def cache_spec(self):
         return self.mixer.cache_spec()
@@ -28,6 +29,8 @@ class PreNormBlock(Part):
             x = self.mixer.forward(ctx, x, cache, residual=x, norm=self.mixer_norm)
         else:
             x = self.mixer.forward(ctx, self.mixer_norm.forward(ctx, x), cache, residual=x)
+        if self.feed_forward is None:       # a layer without a feed-forward
+            return x
         if getattr(self.feed_forward, "takes_norm", False):
             return self.feed_forward.forward(ctx, x, residual=x, norm=self.ff_norm)
         return self.feed_forward.forward(ctx, self.ff_norm.forward(ctx, x), residual=x)

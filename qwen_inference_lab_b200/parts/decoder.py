@@ -32,23 +32,28 @@ class LayerCall:
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab_size, hidden_size, *, name):
-        self.vocab_size, self.hidden_size, self.name = int(vocab_size), int(hidden_size), name
+    def __init__(self, vocab_size, hidden_size, *, name, suffix=".weight"):
+        self.vocab_size, self.hidden_size, self.name, self.suffix = int(vocab_size), int(hidden_size), name, suffix
         self.weight = Param((vocab_size, hidden_size))
 
     def named_params(self):
-        return {self.name + ".weight": self.weight}
+        return {self.name + self.suffix: self.weight}
 
     def forward(self, ctx, token_ids):
-        out = ctx.empty((token_ids.shape[0], self.hidden_size))
+        """Rows of the table in the dtype of the residual stream (the activations' unless the model keeps
+        its stream in float32)."""
+        out = ctx.empty((token_ids.shape[0], self.hidden_size), dtype=ctx.stream_dtype)
         return ops.embed_gather(self.weight.data, token_ids, out)
 
 
 class DecoderModel(Part):
     graph_safe = True      # the model itself only walks its parts; they decide
 
-    def __init__(self, *, config, embedding, layers, order, final_norm, head, max_positions):
+    def __init__(self, *, config, embedding, layers, order, final_norm, head, max_positions, stream_dtype=None):
+        """``stream_dtype``: the dtype of the residual stream where it is not the activations' (float32 for
+        designs that sum their residuals in 32 bits while their products run in bfloat16)."""
         self.config = config
+        self.stream_dtype = stream_dtype
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
         self.order = [call if isinstance(call, LayerCall) else LayerCall(*call) for call in order]
         self.max_positions = int(max_positions)

@@ -4,6 +4,10 @@ gate and up are one stacked product; the activation rounds ``silu(gate)`` to the
 activation dtype before the multiply, as elementwise tensor code does.  In
 bfloat16 the product and the activation are one kernel: the weight-streaming
 kernel for a decode step's few rows, the tcgen05 kernel for prompt portions.
+
+Other activations (``activation``: ``gelu_tanh``, or ``clamped_swish`` with ``limit`` and ``alpha``, see
+``kernels.ops.gated_activation``) and biases on the three projections take the stacked product and an
+activation kernel of their own.
 """
 from __future__ import annotations
 
@@ -17,12 +21,16 @@ from .linear import Linear, StackedLinear
 class GatedMLP(FeedForward):
     graph_safe = True
 
-    def __init__(self, hidden_size, intermediate_size, *, names):
+    def __init__(self, hidden_size, intermediate_size, *, names, activation="silu", limit=0.0, alpha=1.0, bias=False,
+                 suffixes=(".weight", ".bias")):
         """names: dict with keys gate, up, down (projection names without ``.weight``)."""
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r} (known: {sorted(ops.ACTIVATIONS)})")
+        self.activation, self.limit, self.alpha, self.bias = activation, float(limit), float(alpha), bool(bias)
         self.gate_up = StackedLinear(hidden_size, [(names["gate"], intermediate_size),
-                                                   (names["up"], intermediate_size)])
-        self.down = Linear(intermediate_size, hidden_size, name=names["down"])
+                                                   (names["up"], intermediate_size)], bias=bias, suffixes=suffixes)
+        self.down = Linear(intermediate_size, hidden_size, name=names["down"], bias=bias, suffixes=suffixes)
 
         self.pairs8 = False
 
@@ -33,7 +41,8 @@ class GatedMLP(FeedForward):
         super().finalize(device, dtype)
         w = self.gate_up._w
         inner = self.intermediate_size
-        if w.dtype == torch.bfloat16 and inner % 8 == 0 and self.hidden_size % 8 == 0:
+        if w.dtype == torch.bfloat16 and inner % 8 == 0 and self.hidden_size % 8 == 0 \
+                and self.activation == "silu" and not self.bias:
             # rows as groups of [8 gate, 8 up]: a block of the decode GEMM then holds matching gate and up
             # features and applies the activation in its epilogue
             self.gate_up._w = w.view(2, inner // 8, 8, self.hidden_size).transpose(0, 1).reshape(
@@ -45,6 +54,10 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, x, residual=None, norm=None):
         """With ``norm`` x is the block's un-normed input; a decode step's few rows get the norm inside
         the gate/up kernel, longer steps a norm kernel of their own."""
+        if self.activation != "silu" or self.bias:
+            gate_up = self.gate_up.forward(ctx, x, norm=norm)
+            hidden = ops.gated_activation(gate_up, self.activation, limit=self.limit, alpha=self.alpha)
+            return self.down.forward(ctx, hidden, residual=residual)
         rms = norm.as_rms() if norm is not None else None
         if self.pairs8 and ops.small_m_ok(x, self.gate_up._w) and rms is not None and rms[0].dtype == torch.bfloat16:
             hidden = ops.gemm_small_m(x, self.gate_up._w, silu_pairs=True, norm_weight=rms[0], norm_eps=rms[1])

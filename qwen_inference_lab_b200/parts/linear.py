@@ -28,19 +28,20 @@ def _library_mm_f32_out(a, weight):
 class Linear(Part):
     graph_safe = True
 
-    def __init__(self, in_features, out_features, *, name, bias=False, weight=None):
-        """``weight`` may be another part's Param of the same shape (tied embeddings)."""
+    def __init__(self, in_features, out_features, *, name, bias=False, weight=None, suffixes=(".weight", ".bias")):
+        """``weight`` may be another part's Param of the same shape (tied embeddings).  ``suffixes``: what a
+        checkpoint appends to ``name`` for the weight and for the bias."""
         self.in_features, self.out_features = int(in_features), int(out_features)
-        self.name = name
+        self.name, self.suffixes = name, tuple(suffixes)
         if weight is not None and weight.shape != (self.out_features, self.in_features):
             raise ValueError(f"shared weight {weight.shape} does not fit [{out_features}, {in_features}]")
         self.weight = weight if weight is not None else Param((out_features, in_features))
         self.bias = Param((out_features,), init="zeros") if bias else None
 
     def named_params(self):
-        params = {self.name + ".weight": self.weight}
+        params = {self.name + self.suffixes[0]: self.weight}
         if self.bias is not None:
-            params[self.name + ".bias"] = self.bias
+            params[self.name + self.suffixes[1]] = self.bias
         return params
 
     def finalize(self, device, dtype):
@@ -58,8 +59,24 @@ class Linear(Part):
         """``x`` [N, in] -> [N, out]; adds ``residual`` [N, out] when given (may be ``out``).
 
         With ``norm`` (a Norm part) the product is of ``norm(x)``: fused into the kernel where it can be.
+        A float32 ``residual`` under bfloat16 activations (a residual stream kept in float32) gives a
+        float32 result: the product's float32 sums are added to it without a rounding in between.
         """
         weight, bias = self._weight(), self._bias()
+        if residual is not None and residual.dtype == torch.float32 and x.dtype == torch.bfloat16 \
+                and weight.dtype == torch.bfloat16:
+            if norm is not None:
+                x = norm.forward(ctx, x)
+            if ops.small_m_ok(x, weight):
+                return ops.gemm_small_m(x, weight, bias=bias, residual=residual, out=out, out_float32=True)
+            result = _library_mm_f32_out(x, weight)
+            if bias is not None:
+                result += bias.float()
+            ops.add_inplace(result, residual)
+            if out is not None:
+                out.copy_(result)
+                return out
+            return result
         if ops.small_m_ok(x, weight):
             # a decode step's few rows: the engine's weight-streaming kernel
             rms = norm.as_rms() if norm is not None else None
@@ -100,8 +117,9 @@ class StackedLinear(Linear):
     qil/model.py:32-34,38-39; one product over the stack reads the input once).
     """
 
-    def __init__(self, in_features, pieces, *, bias=False):
+    def __init__(self, in_features, pieces, *, bias=False, suffixes=(".weight", ".bias")):
         self.in_features = int(in_features)
+        self.suffixes = tuple(suffixes)
         self.pieces = [(name, int(rows)) for name, rows in pieces]
         self.out_features = sum(rows for _, rows in self.pieces)
         self.parts_w = [Param((rows, in_features)) for _, rows in self.pieces]
@@ -112,9 +130,9 @@ class StackedLinear(Linear):
     def named_params(self):
         params = {}
         for i, (name, _) in enumerate(self.pieces):
-            params[name + ".weight"] = self.parts_w[i]
+            params[name + self.suffixes[0]] = self.parts_w[i]
             if self.parts_b is not None:
-                params[name + ".bias"] = self.parts_b[i]
+                params[name + self.suffixes[1]] = self.parts_b[i]
         return params
 
     def finalize(self, device, dtype):

@@ -26,3 +26,24 @@ class RMSNorm(Norm):
 
     def as_rms(self):
         return self.weight.data, self.eps
+
+
+class ExactRMSNorm(Norm):
+    """``y = x / sqrt(mean(x^2) + eps) * (offset + w)`` with float32 arithmetic and a single rounding.
+
+    ``offset`` 1 is for weights stored around zero.  The input may be a float32 residual stream under
+    bfloat16 activations: the result has the activation dtype (``ctx.dtype``).  ``suffix`` is what the
+    checkpoint appends to ``name``.
+    """
+    graph_safe = True
+
+    def __init__(self, width, eps, *, name, offset=0.0, suffix=".weight", optional=False):
+        self.width, self.eps, self.offset, self.name, self.suffix = int(width), float(eps), float(offset), name, suffix
+        init = ("normal", 0.05) if offset else ("norm", 0.05)
+        self.weight = Param((width,), init=init[0], std=init[1], optional=optional)
+
+    def named_params(self):
+        return {self.name + self.suffix: self.weight}
+
+    def forward(self, ctx, x, rows=None):
+        return ops.rmsnorm_exact(x, self.weight.data, self.eps, self.offset, out_dtype=ctx.dtype, rows=rows)

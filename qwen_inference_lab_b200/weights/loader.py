@@ -79,7 +79,8 @@ def load_weights(model, directory, *, device, dtype, keep_stored_32bit=False) ->
                     continue
                 param.data = value
     # a tied parameter is satisfied by either of its names; a mis-shaped tensor is reported as such, not as missing
-    missing = sorted(name for name, param in expected.items() if param.data is None and id(param) not in mis_shaped)
+    missing = sorted(name for name, param in expected.items()
+                     if param.data is None and id(param) not in mis_shaped and not param.optional)
     problems = []
     if missing:
         problems.append(f"missing tensors ({len(missing)}): {missing}")
