@@ -382,6 +382,252 @@ def run_ours(args):
     print(json.dumps(line), flush=True)
 
 
+
+# --------------------------------------------------------------------------- Virulix beside dense Qwen3
+def _virulix_sizes(width, heads, kv_heads, dim, gla_heads, gla_vdim, dense_ff, experts, top, expert_ff, shared_ff, vocab):
+    """Eight layers that use every mechanism of the design at one width."""
+    attention = lambda **extra: dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                     q_temp=dict(coef=0.1, every=256), **extra)
+    gla = dict(heads=gla_heads, dim=dim, vdim=gla_vdim, tau=16.0, rank=16)
+    moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff, limit=7.0),
+               shared=dict(ff=shared_ff, limit=7.0))
+    dense = dict(kind="dense", ff=dense_ff)
+    layers = [dict(type="attention", mixer=attention(), mlp=dense), dict(type="gla", mixer=gla, mlp=moe),
+              dict(type="attention", mixer=attention(), mlp=moe), dict(type="gla", mixer=gla, mlp=moe),
+              dict(type="attention", mixer=attention(kv_from=2), mlp=moe), dict(type="gla", mixer=gla, mlp=dense),
+              dict(type="attention", mixer=attention(), mlp=dense), dict(type="gla", mixer=gla, mlp=moe)]
+    return dict(architecture="Virulix", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=layers)
+
+
+VIRULIX_SHAPES = {
+    # name: (Virulix sizes, the dense Qwen3 of equal width, heads, head size, layer count and vocabulary)
+    "2048": dict(width=2048, heads=16, kv_heads=4, dim=128, gla_heads=4, gla_vdim=256, dense_ff=6144, experts=32,
+                 top=4, expert_ff=768, shared_ff=1536, vocab=32768),
+    "4096": dict(width=4096, heads=32, kv_heads=8, dim=128, gla_heads=8, gla_vdim=256, dense_ff=12288, experts=64,
+                 top=6, expert_ff=1024, shared_ff=2048, vocab=32768),
+}
+
+
+def _timed(torch, fn, reps=12, warmup=3, flush=None):
+    """Median milliseconds of ``fn`` on the device, an L2 flush before every timed call."""
+    times = []
+    for i in range(warmup + reps):
+        if flush is not None:
+            flush.zero_()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+class _ModelBench:
+    """Whole-model prompt and decode steps of any model of the engine, timed on the device."""
+
+    def __init__(self, model, vocab):
+        import torch
+        self.torch, self.model, self.vocab = torch, model, vocab
+
+    def _parts(self, tokens, requests):
+        from qwen_inference_lab_b200.cache import CacheManager
+        from qwen_inference_lab_b200.engine import StepRunner
+        pages = requests * ((tokens + PAGE_SIZE - 1) // PAGE_SIZE + 2)
+        cache = CacheManager(self.model.cache_specs(), num_pages=pages, page_size=PAGE_SIZE, max_requests=requests,
+                             max_context=pages * PAGE_SIZE, dtype=self.model.dtype, device=self.model.device)
+        return cache, StepRunner(self.model, cache, max_step_tokens=max(tokens, 64))
+
+    def prefill(self, tokens_n, flush):
+        from qwen_inference_lab_b200.engine import StepEntry
+        torch = self.torch
+        cache, runner = self._parts(tokens_n, 1)
+        prompt = torch.randint(0, self.vocab, (tokens_n,), generator=torch.Generator().manual_seed(2)).tolist()
+        def once():
+            cache.admit("p")
+            runner.run([StepEntry("p", prompt, [tokens_n - 1])])
+            cache.release("p")
+        return _timed(torch, once, reps=7, warmup=3, flush=flush)
+
+    def decode(self, batch, context, steps, warmup):
+        from qwen_inference_lab_b200.engine import StepEntry
+        torch = self.torch
+        cache, runner = self._parts(context + steps + warmup + 2, batch)
+        for g in cache.kv_groups:
+            g.storage.normal_(0.0, 0.5)
+        for rid in range(batch):
+            cache.admit(rid)
+            cache.ensure(rid, context)
+            cache.advance(rid, context)
+        tokens = torch.randint(0, self.vocab, (steps + warmup, batch), generator=torch.Generator().manual_seed(1)).tolist()
+        one = lambda i: runner.run([StepEntry(rid, [tokens[i][rid]], [0]) for rid in range(batch)])
+        for i in range(warmup):
+            one(i)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(warmup, warmup + steps):
+            logits = one(i)
+        stop.record()
+        torch.cuda.synchronize()
+        assert torch.isfinite(logits).all()
+        return start.elapsed_time(stop) / steps
+
+
+def _mixer_kernels(torch, model, sizes, pk, tokens_n, batch, context, flush, qwen):
+    """The mixers' own kernels alone, with what the roofline allows: (name, ms, fraction of the measured peak)."""
+    from qwen_inference_lab_b200.cache import CacheManager
+    from qwen_inference_lab_b200.engine import StepEntry, StepRunner
+    from qwen_inference_lab_b200.kernels import ops
+    from tests.harness import OnePartModel
+    rows = []
+    H, G, d = sizes["heads"], sizes["kv_heads"], sizes["dim"]
+    tflops, gbs = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+
+    def run_part(part, body, hidden, prompt_tokens, decode_batch, decode_context):
+        """(ms of a whole prompt, ms of a step of single tokens) of ``body`` over the step function."""
+        shell = OnePartModel(part, hidden, torch.bfloat16, body)
+        shell.inputs = torch.randn(4096, hidden, device="cuda").to(torch.bfloat16)
+        pages = (decode_batch + 1) * ((max(prompt_tokens, decode_context) + PAGE_SIZE) // PAGE_SIZE + 2)
+        cache = CacheManager(shell.cache_specs(), num_pages=pages, page_size=PAGE_SIZE, max_requests=decode_batch + 1,
+                             max_context=pages * PAGE_SIZE, dtype=torch.bfloat16, device="cuda")
+        for g in cache.kv_groups:
+            g.storage.normal_(0.0, 0.5)
+        runner = StepRunner(shell, cache, max_step_tokens=prompt_tokens, use_graphs=False)
+        ids = [i % 4096 for i in range(prompt_tokens)]
+        def prompt():
+            cache.admit("p")
+            runner.run([StepEntry("p", ids, [])])
+            cache.release("p")
+        for rid in range(decode_batch):
+            cache.admit(rid)
+            cache.ensure(rid, decode_context)
+            cache.advance(rid, decode_context)
+        single = lambda: runner.run([StepEntry(rid, [rid], []) for rid in range(decode_batch)])
+        return prompt, single, shell
+
+    class Timer:
+        """Times the part's kernel inside ``body`` with events of its own, so that the projections around it stay out."""
+        def __init__(self):
+            self.ms = []
+        def __call__(self, fn):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = fn()
+            stop.record()
+            self.ms.append((start, stop))
+            return out
+        def median(self, skip):
+            torch.cuda.synchronize()
+            values = [a.elapsed_time(b) for a, b in self.ms[skip:]]
+            self.ms = []
+            return statistics.median(values)
+
+    def measure(name_prefix, part, hidden, kernel_of, flops_prompt, bytes_decode):
+        timer = Timer()
+        def body(ctx, x, view):
+            return kernel_of(ctx, x, view, timer)
+        prompt, single, shell = run_part(part, body, hidden, tokens_n, batch, context)
+        for i in range(8):
+            flush.zero_()
+            prompt()
+            shell.outputs.clear()
+        ms = timer.median(3)
+        rows.append((f"{name_prefix} prompt {tokens_n}", ms, flops_prompt / (ms * 1e-3) / tflops, "of the bf16 peak"))
+        for i in range(12):
+            flush.zero_()
+            single()
+            shell.outputs.clear()
+        ms = timer.median(4)
+        rows.append((f"{name_prefix} decode b{batch} c{context}", ms, bytes_decode / (ms * 1e-3) / gbs, "of the copy bandwidth"))
+
+    def attention_kernel(mixer):
+        def kernel(ctx, x, view, timer):
+            q = x[:, :H * d].contiguous()
+            out = torch.empty_like(q)
+            timer(lambda: mixer._attend(ctx, q, view, out))
+            return out
+        return kernel
+
+    layers = model.layers
+    attention = next(l.mixer for l in layers if hasattr(l.mixer, "plain_tail") and not l.mixer.reads_shared_cache)
+    attn_flops = 4.0 * H * d * tokens_n * (tokens_n + 1) / 2
+    attn_bytes = batch * context * 2 * G * d * 2
+    measure("virulix attention (distance bias)", attention, H * d, attention_kernel(attention), attn_flops, attn_bytes)
+    measure("qwen3 attention", qwen.layers[0].mixer, H * d, attention_kernel(qwen.layers[0].mixer), attn_flops, attn_bytes)
+
+    gla = next(l.mixer for l in layers if hasattr(l.mixer, "decay_rank"))
+    gh, gd, ge = gla.n_heads, gla.key_dim, gla.value_dim
+    width = gla.projection.out_features
+    def gla_kernel(ctx, x, view, timer):
+        projected = x[:, :width].contiguous()
+        mixed = torch.empty((x.shape[0], gh * ge), dtype=x.dtype, device=x.device)
+        scratch = torch.empty((x.shape[0], gh * ge), dtype=torch.float32, device=x.device) if gla._needs_scratch else None
+        timer(lambda: ops.gla_scan(projected, gla.columns, gla.decay_up.data, gla.decay_bias.data, gla.tau, gla.q_scale,
+                                   gla.norm_weight.data, gla.norm_eps, view.slots, ctx.seg_start, ctx.seg_len, ctx.seg_row,
+                                   ctx.n_segments, gh, gd, ge, mixed, scratch=scratch))
+        return mixed
+    # the recurrence is float32 on the CUDA cores by the design: its prompt bound is the float32 FMA rate
+    fma_peak = 148 * 128 * 2 * 1.9e9
+    timer_rows = len(rows)
+    measure("virulix gla scan", gla, max(width, 8), gla_kernel, 5.0 * gh * gd * ge * tokens_n, batch * gh * gd * ge * 4 * 2)
+    name, ms, _, _ = rows[timer_rows]
+    rows[timer_rows] = (name, ms, 5.0 * gh * gd * ge * tokens_n / (ms * 1e-3) / fma_peak, "of the float32 FMA rate (72 TFLOP/s nominal)")
+
+    moe = next(l.feed_forward for l in layers if hasattr(l.feed_forward, "n_experts"))
+    W, ff, E, top = moe.hidden_size, moe.expert_size, moe.n_experts, moe.top
+    def moe_kernel(ctx, x, view, timer):
+        h = x[:, :W].contiguous()
+        chosen, weights = ops.moe_route(h, moe.router.data, moe.router_bias.data, top)
+        return timer(lambda: ops.moe_experts(h, chosen, weights, moe._gate, moe._up, moe._down, moe.activation,
+                                             limit=moe.limit, alpha=moe.alpha))
+    measure("virulix routed experts", moe, W, moe_kernel, 2.0 * tokens_n * top * 3 * ff * W,
+            min(E, batch * top) * 3 * ff * W * 2)
+    dense = qwen.layers[0].feed_forward
+    def dense_kernel(ctx, x, view, timer):
+        h = x[:, :W].contiguous()
+        return timer(lambda: dense.forward(ctx, h))
+    inner = dense.intermediate_size
+    measure("qwen3 gated mlp", dense, W, dense_kernel, 2.0 * tokens_n * 3 * inner * W, 3 * inner * W * 2)
+    return rows
+
+
+def run_virulix(args):
+    """Prefill and decode of Virulix at sizes like a real model's layers, beside dense Qwen3 of equal width,
+    heads, layer count and vocabulary, and the mixers' own kernels against their rooflines."""
+    import torch
+    from qwen_inference_lab_b200.config import Qwen3Config, VirulixConfig
+    from qwen_inference_lab_b200.loading import random_model
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in ([args.virulix_shape] if args.virulix_shape else sorted(VIRULIX_SHAPES)):
+        sizes = VIRULIX_SHAPES[name]
+        virulix = random_model(VirulixConfig.from_dict(_virulix_sizes(**sizes)), seed=0, device="cuda", dtype=torch.bfloat16)
+        qwen_cfg = dict(QWEN3_8B, vocab_size=sizes["vocab"], hidden_size=sizes["width"], intermediate_size=sizes["dense_ff"],
+                        num_hidden_layers=8, num_attention_heads=sizes["heads"], num_key_value_heads=sizes["kv_heads"],
+                        head_dim=sizes["dim"])
+        qwen = random_model(Qwen3Config.from_dict(dict(qwen_cfg, model_type="qwen3")), seed=0, device="cuda", dtype=torch.bfloat16)
+        result = {"workload": "virulix", "width": sizes["width"], "layers": 8, "dtype": "bfloat16",
+                  "peaks": "of measured" if pk["source"] == "measured" else "of fallback", "models": {}, "kernels": []}
+        for label, model in (("virulix", virulix), ("qwen3", qwen)):
+            bench = _ModelBench(model, sizes["vocab"])
+            entry = {}
+            for tokens_n in (512, 2048):
+                ms = bench.prefill(tokens_n, flush)
+                entry[f"prefill_{tokens_n}"] = {"ms": round(ms, 3), "tokens_per_s": round(tokens_n / ms * 1e3, 1)}
+            for batch, context in ((1, 2048), (8, 2048), (32, 2048)):
+                ms = bench.decode(batch, context, args.steps, args.warmup)
+                entry[f"decode_b{batch}_c{context}"] = {"ms": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1)}
+            result["models"][label] = entry
+        for kernel, ms, frac, of in _mixer_kernels(torch, virulix, sizes, pk, 2048, 8, 2048, flush, qwen):
+            result["kernels"].append({"kernel": kernel, "ms": round(ms, 4), "frac": round(frac, 4), "of": of})
+        print(json.dumps(result), flush=True)
+        del virulix, qwen
+        torch.cuda.empty_cache()
+
+
 # --------------------------------------------------------------------------- the reference
 def run_reference(args):
     ref = ROOT / "baseline" / "_ref"
@@ -469,9 +715,12 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     parser.add_argument("--quick", action="store_true", help="skip the batch 1 and 64 points")
-    parser.add_argument("--only", choices=["decode", "prefill", "mixed"], default=None,
+    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "virulix"], default=None,
                         help="run just this part and print its result instead of the JSON line; mixed = 64 requests "
-                             "with prompts of 16 to 2048 tokens and 128 new tokens each through Engine.generate")
+                             "with prompts of 16 to 2048 tokens and 128 new tokens each through Engine.generate; "
+                             "virulix = the Virulix design beside dense Qwen3 of equal size, and its mixers' kernels")
+    parser.add_argument("--virulix-shape", choices=sorted(VIRULIX_SHAPES), default=None,
+                        help="width of --only virulix (default: all)")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes (default: Qwen3-8B)")
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request (profiling aid)")
@@ -485,6 +734,9 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.only == "virulix":
+        run_virulix(args)
+        return 0
     run_ours(args)
     return 0
 

@@ -94,6 +94,8 @@ struct AttnParams {
     int table_stride;
     int n_q_heads, n_kv_heads, page_size, num_pages, window;
     float scale_log2;         // head_dim^-1/2 * log2(e)
+    // null, or one slope per query head, times log2(e): score = q.k * scale - slope_h * (query position - key position)
+    const float* slopes_log2;
 };
 
 // Where the key row of position ``pos`` of one kv head starts, in units of 16 bytes from the layer's
@@ -145,6 +147,7 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     const int hi = pos0 + rows - 1;
     const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
     const int* table = p.block_table + (size_t)info.w * p.table_stride;
+    const float slope = p.slopes_log2 != nullptr ? p.slopes_log2[head] : 0.f;
 
     {   // queries of this tile: two threads per row
         const int row = tid >> 1, half = tid & 1;
@@ -223,7 +226,7 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
         // the first row's position and inside the last row's window needs no mask.
         float tmax_a = -INFINITY, tmax_b = -INFINITY;
         const bool full = (tile + 1) * KV_TILE - 1 <= pos0 && (p.window == 0 || tile * KV_TILE > hi - p.window);
-        if (full) {
+        if (full && slope == 0.f) {
 #pragma unroll
             for (int nt = 0; nt < KV_TILE / 8; ++nt) {
 #pragma unroll
@@ -238,8 +241,8 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
                 for (int e = 0; e < 4; ++e) {
                     const int key = tile * KV_TILE + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = (e < 2) ? pos_a : pos_b;
-                    const bool ok = key <= pos && (p.window == 0 || key > pos - p.window);
-                    const float v = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+                    const bool ok = full || (key <= pos && (p.window == 0 || key > pos - p.window));
+                    const float v = ok ? fmaf((float)(key - pos), slope, s[nt][e] * p.scale_log2) : -INFINITY;
                     s[nt][e] = v;
                     if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
                 }
@@ -485,6 +488,12 @@ __device__ __forceinline__ void attn_decode_span_block(
     const int chunks = (group + 15) / 16;
     const int kv_head = block_x / chunks, g0 = (block_x % chunks) * 16;
     const int gcount = min(16, group - g0);
+    float slope_a = 0.f, slope_b = 0.f;       // of the query heads on this lane's two rows of the score tiles
+    if (p.slopes_log2 != nullptr) {
+        const int row = (threadIdx.x & 31) >> 2;
+        if (row < gcount) slope_a = p.slopes_log2[kv_head * group + g0 + row];
+        if (row + 8 < gcount) slope_b = p.slopes_log2[kv_head * group + g0 + row + 8];
+    }
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
     const int hi = pos;
@@ -619,14 +628,14 @@ __device__ __forceinline__ void attn_decode_span_block(
         __syncwarp();                // every lane has read the keys: their rows take tile t + 2
         if (tile + 2 <= last_tile) issue_rows(off2, my_k + buf * BUFFER, 0);
         cp_async_commit();
-        // every row is the same position: one mask for all
+        // every row is the same position: one mask for all (a row is a query head: each has its slope)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = tile * KV_TILE + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
                 const bool ok = key <= hi && key >= lo;
-                s[nt][e] = ok ? s[nt][e] * p.scale_log2 : -INFINITY;
+                s[nt][e] = ok ? fmaf((float)(key - hi), e < 2 ? slope_a : slope_b, s[nt][e] * p.scale_log2) : -INFINITY;
             }
         }
         float tmax_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -785,6 +794,7 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.slopes_log2 = nullptr;
     return 0;
 }
 
@@ -826,13 +836,16 @@ extern "C" int qil_attn_head_dim() { return D; }
 extern "C" int qil_attn_max_decode_span() { return MAX_DECODE_SPAN; }
 
 // tile_info: int32 [n_tiles, 4] = (first token, its absolute position, rows <= 64, block-table row).
-extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
-                                const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
-                                int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+// slopes_log2: null, or float32 [n_q_heads]: a distance bias per query head (see AttnParams).
+extern "C" int qil_attn_prefill_biased(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                       const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                       int page_size, int num_pages, int window, float scale,
+                                       const float* slopes_log2, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
+    p.slopes_log2 = slopes_log2;
     if (n_tiles > 65535) QIL_REFUSE("attention: %d query tiles in one launch; at most 65535", n_tiles);
     if ((uintptr_t)tile_info & 15) QIL_REFUSE("attention: tile_info must be 16-byte aligned");
     const int smem = ((Q_IN_REGS ? 0 : Q_TILE) + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
@@ -844,6 +857,13 @@ extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const 
     }
     attn_prefill_kernel<<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                int page_size, int num_pages, int window, float scale, cudaStream_t stream) {
+    return qil_attn_prefill_biased(q, kv, out, tile_info, n_tiles, block_table, table_stride, n_q_heads, n_kv_heads,
+                                   page_size, num_pages, window, scale, nullptr, stream);
 }
 
 // decode_info: int32 [n_decode, 4] = (token, its absolute position, block-table row, 0).
@@ -859,11 +879,12 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
                          float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                          int page_size, int num_pages, int window, float scale, const DecodeTail& tail,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const float* slopes_log2 = nullptr) {
     if (n_decode <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
+    p.slopes_log2 = slopes_log2;
     if (check_decode_span(span_len, n_spans)) return -1;
     if (part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
@@ -889,6 +910,17 @@ extern "C" int qil_attn_decode(const void* q, const void* kv, void* out, const i
     DecodeTail none = {};
     return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream);
+}
+
+// The same with a distance bias per query head (slopes_log2: float32 [n_q_heads], see AttnParams).
+extern "C" int qil_attn_decode_biased(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                                      float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
+                                      const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                      int page_size, int num_pages, int window, float scale, const float* slopes_log2,
+                                      cudaStream_t stream) {
+    DecodeTail none = {};
+    return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
+                         table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream, slopes_log2);
 }
 
 // The same over the raw output of the query/key/value projection, for steps in which every token is a single

@@ -13,8 +13,9 @@
 //   down      y[p] = weight[p] * (h W_down[e]^T), float32, written at the pair's own place.
 //   combine   out[t] = residual[t] + sum over slots of y[t * top + slot], in slot order.
 //
-// The products run on the CUDA cores with float32 FMA, each output element summing over k in ascending
-// order with one accumulator: a pair's result does not depend on which rows share its tile.
+// In float32 the products run on the CUDA cores with float32 FMA, each output element summing over k in
+// ascending order with one accumulator: a pair's result does not depend on which rows share its tile.
+// bfloat16 rows and weights whose width is a multiple of 8 take the tensor cores (further down).
 // The activation is the clamped swish of gated_activation.cu (kind 2) or silu (kind 0).
 #include "common.cuh"
 
@@ -247,6 +248,132 @@ moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w
     }
 }
 
+// ------------------------------------------------------------------ the same products on the tensor cores
+// bfloat16 rows and weights, float32 accumulators (mma.sync m16n8k16).  A block takes the same 64-row tile of
+// one expert and 64 output features; its four warps own 16 rows each.  Rows and weights move through two
+// stages of 32 k-values with cp.async; rows past the tile's end and k-values past K arrive as zeros.
+#define MOE_TK 32
+#define MOE_LDS (MOE_TK + 8)       // row stride in elements: rows start 16 bytes apart mod 128
+
+__device__ __forceinline__ void moe_cp_async16(void* smem, const void* gmem, bool valid) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void moe_ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void moe_mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool DUAL>
+__global__ void __launch_bounds__(128)
+moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
+                      const int* __restrict__ tiles, const int* __restrict__ info,
+                      const int* __restrict__ sorted_pairs, int top, const float* __restrict__ pair_weight,
+                      bf16* __restrict__ hidden, float* __restrict__ y, int n_out, int K, int kind, float limit,
+                      float alpha) {
+    __shared__ __align__(16) bf16 sA[2][MOE_BM][MOE_LDS];
+    __shared__ __align__(16) bf16 sB0[2][MOE_BN][MOE_LDS];
+    __shared__ __align__(16) bf16 sB1[DUAL ? 2 : 1][DUAL ? MOE_BN : 1][MOE_LDS];
+    __shared__ int src_row[MOE_BM];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const int tile = blockIdx.y;
+    if (tile >= info[0]) return;
+    const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * MOE_BN;
+    if (tid < MOE_BM) src_row[tid] = tid < rows ? (DUAL ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
+    __syncthreads();
+    const bf16* e0 = w0 + (size_t)expert * n_out * K;
+    const bf16* e1 = DUAL ? w1 + (size_t)expert * n_out * K : nullptr;
+
+    auto issue = [&](int stage, int k0) {
+        // 64 rows x 4 pieces of 16 bytes per operand: two pieces a thread
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int idx = tid + it * 128;
+            const int r = idx >> 2, piece = idx & 3, k = k0 + piece * 8;
+            const bool in_k = k < K;
+            const bool a_ok = in_k && src_row[r] >= 0;
+            moe_cp_async16(&sA[stage][r][piece * 8], A + (a_ok ? (size_t)src_row[r] * lda + k : 0), a_ok);
+            const bool b_ok = in_k && n0 + r < n_out;
+            moe_cp_async16(&sB0[stage][r][piece * 8], e0 + (b_ok ? (size_t)(n0 + r) * K + k : 0), b_ok);
+            if (DUAL) moe_cp_async16(&sB1[stage][r][piece * 8], e1 + (b_ok ? (size_t)(n0 + r) * K + k : 0), b_ok);
+        }
+    };
+    float acc0[MOE_BN / 8][4], acc1[DUAL ? MOE_BN / 8 : 1][4];
+#pragma unroll
+    for (int i = 0; i < MOE_BN / 8; ++i) { acc0[i][0] = acc0[i][1] = acc0[i][2] = acc0[i][3] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < (DUAL ? MOE_BN / 8 : 1); ++i) { acc1[i][0] = acc1[i][1] = acc1[i][2] = acc1[i][3] = 0.f; }
+
+    const int steps = (K + MOE_TK - 1) / MOE_TK;
+    issue(0, 0);
+    asm volatile("cp.async.commit_group;\n" ::);
+    for (int step = 0; step < steps; ++step) {
+        const int stage = step & 1;
+        if (step + 1 < steps) issue(stage ^ 1, (step + 1) * MOE_TK);
+        asm volatile("cp.async.commit_group;\n" ::);
+        asm volatile("cp.async.wait_group 1;\n" ::);
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < MOE_TK / 16; ++ks) {
+            unsigned a[4];
+            moe_ldmatrix_x4(a[0], a[1], a[2], a[3],
+                            &sA[stage][warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int np = 0; np < MOE_BN / 16; ++np) {
+                unsigned b0, b1, b2, b3;
+                moe_ldmatrix_x4(b0, b1, b2, b3,
+                                &sB0[stage][np * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+                moe_mma_bf16(acc0[2 * np], a, b0, b1);
+                moe_mma_bf16(acc0[2 * np + 1], a, b2, b3);
+                if (DUAL) {
+                    moe_ldmatrix_x4(b0, b1, b2, b3,
+                                    &sB1[stage][np * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+                    moe_mma_bf16(acc1[2 * np], a, b0, b1);
+                    moe_mma_bf16(acc1[2 * np + 1], a, b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = warp * 16 + (lane >> 2) + half * 8;
+        if (r >= rows) continue;
+        const int pair = DUAL ? 0 : sorted_pairs[row0 + r];
+        const float scale = DUAL ? 1.f : pair_weight[pair];
+#pragma unroll
+        for (int nt = 0; nt < MOE_BN / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int n = n0 + nt * 8 + (lane & 3) * 2 + e;
+                if (n >= n_out) continue;
+                if (DUAL) {
+                    const float g = round_to<bf16>(acc0[nt][half * 2 + e]), u = round_to<bf16>(acc1[nt][half * 2 + e]);
+                    hidden[(size_t)(row0 + r) * n_out + n] = __float2bfloat16_rn(expert_activation(kind, g, u, limit, alpha));
+                } else {
+                    y[(size_t)pair * n_out + n] = scale * acc0[nt][half * 2 + e];
+                }
+            }
+        }
+    }
+}
+
+static bool moe_tensor_cores_usable(int act_dtype, int weight_dtype, int lda, int K, const void* a, const void* b,
+                                    const void* c) {
+    return act_dtype == QIL_BF16 && weight_dtype == QIL_BF16 && K % 8 == 0 && lda % 8 == 0
+        && (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c) & 15) == 0;
+}
+
 // ------------------------------------------------------------------ combine
 template <typename R>
 __global__ void __launch_bounds__(256)
@@ -302,6 +429,12 @@ extern "C" int qil_moe_gate_up(const void* x, int lda, const void* gate_w, const
     if (max_tiles <= 0) return 0;
     if (max_tiles > 65535) QIL_REFUSE("moe_gate_up: %d row tiles are too many for one launch", max_tiles);
     dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
+    if (moe_tensor_cores_usable(act_dtype, weight_dtype, lda, K, x, gate_w, up_w)) {
+        qil_launch_chained(moe_expert_mma_kernel<true>, grid, dim3(128), 0, stream, (const bf16*)x, lda,
+                           (const bf16*)gate_w, (const bf16*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
+                           (bf16*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha);
+        QIL_CHECK_LAUNCH();
+    }
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         (qil_launch_chained(moe_expert_gemm_kernel<T, W, true>, grid, dim3(256), 0, stream, (const T*)x, lda,
                             (const W*)gate_w, (const W*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
@@ -315,6 +448,12 @@ extern "C" int qil_moe_down(const void* hidden, const void* down_w, const int* t
     if (max_tiles <= 0) return 0;
     if (max_tiles > 65535) QIL_REFUSE("moe_down: %d row tiles are too many for one launch", max_tiles);
     dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
+    if (moe_tensor_cores_usable(act_dtype, weight_dtype, K, K, hidden, down_w, down_w)) {
+        qil_launch_chained(moe_expert_mma_kernel<false>, grid, dim3(128), 0, stream, (const bf16*)hidden, K,
+                           (const bf16*)down_w, (const bf16*)nullptr, tiles, info, sorted_pairs, 1, pair_weight,
+                           (bf16*)nullptr, y, n_out, K, 0, 0.f, 0.f);
+        QIL_CHECK_LAUNCH();
+    }
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         (qil_launch_chained(moe_expert_gemm_kernel<T, W, false>, grid, dim3(256), 0, stream, (const T*)hidden, K,
                             (const W*)down_w, (const W*)nullptr, tiles, info, sorted_pairs, 1, pair_weight,

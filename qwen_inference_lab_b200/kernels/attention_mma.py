@@ -187,28 +187,38 @@ def decode_scratch(ctx, n_decode, n_q_heads, n_spans, head_dim):
     return scratch
 
 
+def _check_slopes(slopes_log2, n_q_heads):
+    if slopes_log2 is not None and (slopes_log2.dtype != torch.float32 or slopes_log2.shape != (n_q_heads,)
+                                    or not slopes_log2.is_cuda or not slopes_log2.is_contiguous()):
+        raise KernelError("attention: the distance slopes must be float32 [query heads] on the device")
+
+
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, head_dim, page_size, window,
-            scale):
-    """tile_info int32 [n_tiles * 4]: (first token, its position, rows <= 64, block-table row) per tile."""
+            scale, slopes_log2=None):
+    """tile_info int32 [n_tiles * 4]: (first token, its position, rows <= 64, block-table row) per tile.
+    ``slopes_log2`` float32 [Hq]: slope_h * log2(e) of a bias slope_h * (query position - key position) that is
+    taken off the scaled score."""
     lib = library(head_dim)
-    _check(lib, lib.qil_attn_prefill(
+    _check_slopes(slopes_log2, n_q_heads)
+    _check(lib, lib.qil_attn_prefill_biased(
         _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
         c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
-        c_float(scale), _stream()), "attention (prompt portions)")
+        c_float(scale), _p(slopes_log2), _stream()), "attention (prompt portions)")
 
 
 def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
-           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None):
+           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None, slopes_log2=None):
     """decode_info int32 [n_decode * 4]: (token, its position, block-table row, the step's longest context)
     per single token.  A negative ``span_len``: the kernels cut the step's longest context into ``n_spans``
     equal spans of at most ``-span_len`` positions (see ``plan_spans``).  ``tickets``: int32 zeros, one per
     (token, query head) or more (``decode_scratch``): the last block of a token's spans merges them; None: a
     second kernel does."""
     lib = library(head_dim)
-    _check(lib, lib.qil_attn_decode(
+    _check_slopes(slopes_log2, n_q_heads)
+    _check(lib, lib.qil_attn_decode_biased(
         _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
         c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
-        c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _stream()),
+        c_int(page_size), c_int(pages.shape[0]), c_int(window), c_float(scale), _p(slopes_log2), _stream()),
         "attention (single tokens)", kernels=1 if tickets is not None else 2)
 
 
@@ -255,8 +265,9 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
         "attention (single tokens from the projection)", kernels=1 if tickets is not None else 2)
 
 
-def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
-    """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values."""
+def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, slopes_log2=None):
+    """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values.
+    ``slopes_log2``: see ``prefill`` (the tensor-memory kernel has no such bias: all tiles then take the tiled one)."""
     if q.dtype != torch.bfloat16 or cache.pages.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
     if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
@@ -264,7 +275,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
     arrays, counts = step_plan(ctx)
     n_tiles, n_big, n_rest, n_decode = (counts[name] // 4 for name in
                                         ("tile_info", "big_tile_info", "rest_tile_info", "decode_info"))
-    if n_big and attention_tc.supports(head_dim, cache.page_size, window):
+    if n_big and slopes_log2 is None and attention_tc.supports(head_dim, cache.page_size, window):
         # whole 128-token tiles on tcgen05 with the accumulators in tensor memory, the leftovers below
         attention_tc.prefill(q, cache.pages, out, arrays["big_tile_info"], n_big, cache.block_table,
                              n_q_heads, n_kv_heads, cache.page_size, scale)
@@ -273,7 +284,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
                     n_kv_heads, head_dim, cache.page_size, window, scale)
     elif n_tiles:
         prefill(q, cache.pages, out, arrays["tile_info"], n_tiles, cache.block_table, n_q_heads, n_kv_heads,
-                head_dim, cache.page_size, window, scale)
+                head_dim, cache.page_size, window, scale, slopes_log2)
     if n_decode:
         n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                            getattr(ctx, "min_context", 0) or None)
@@ -281,4 +292,4 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale):
         if not merge_in_kernel(n_decode, n_q_heads, n_kv_heads, head_dim):
             tickets = None
         decode(q, cache.pages, out, arrays["decode_info"], n_decode, part_o, part_ml, n_spans, -longest_span,
-               cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets)
+               cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets, slopes_log2)

@@ -75,7 +75,7 @@ class GroupedQueryAttention(Mixer):
                            or self.q_temperature is not None)
         if self.plain_tail and (qk_norm_eps is not None or position is not None):
             raise ValueError("distance slopes, query temperature and a value size of its own go without q/k norms and rotation")
-        self._slopes = None
+        self._slopes = self._slopes_log2 = None
         pieces = [(names["q"], n_q_heads * head_dim)]
         if not self.reads_shared_cache:
             pieces += [(names["k"], n_kv_heads * head_dim), (names["v"], n_kv_heads * self.v_head_dim)]
@@ -106,6 +106,7 @@ class GroupedQueryAttention(Mixer):
             self.q_norm.data, self.k_norm.data = self.q_norm.data.float(), self.k_norm.data.float()
         if self.distance_slopes is not None:
             self._slopes = torch.tensor(self.distance_slopes, dtype=torch.float32, device=device)
+            self._slopes_log2 = (self._slopes.double() * 1.4426950408889634).float().contiguous()
 
     def step_planners(self):
         return {**super().step_planners(), _PLANNER.key: _PLANNER}
@@ -165,10 +166,10 @@ class GroupedQueryAttention(Mixer):
         return self.out.forward(ctx, attended, residual=residual)
 
     def _attend(self, ctx, q, cache, out):
-        if not self.plain_tail and q.dtype == torch.bfloat16 \
+        if q.dtype == torch.bfloat16 and self.v_head_dim == self.head_dim \
                 and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads):
             attention_mma.attend(ctx, q, cache, out, self.n_q_heads, self.n_kv_heads, self.head_dim,
-                                 self.window, self.scale)
+                                 self.window, self.scale, self._slopes_log2)
             return
         ops.attention_generic(q, cache.pages, out, ctx.positions, ctx.token_row, cache.block_table,
                               self.n_q_heads, self.n_kv_heads, self.head_dim, cache.page_size,

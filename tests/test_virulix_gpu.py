@@ -155,6 +155,42 @@ def test_a_far_key_that_outweighs_its_distance(dtype, far):
     close(out, expected[picks].reshape(len(picks), -1), dtype, scale=0.3)
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("query", [259, 299])
+@pytest.mark.parametrize("far", [0, 5, 63, 64, 127, 128, 200])
+def test_a_far_key_through_the_mixer_in_prompts_and_in_decoding(dtype, far, query):
+    """The same through the mixer (in bfloat16 with equal head sizes: the tensor-core kernels): projections that
+    copy slices of the input, so that the test sets queries, keys and values through it.  The far key stands out
+    for the query at position 259 (inside a prompt portion) or 299 (a single decoded token)."""
+    from qwen_inference_lab_b200.parts import GroupedQueryAttention
+    from qwen_inference_lab_b200.models.virulix import BARE, distance_slopes
+    heads, kv_heads, d, T = 4, 2, 16, 300
+    part = GroupedQueryAttention(128, heads, kv_heads, d, names={k: "m." + k for k in "qkvo"}, bias=True, out_bias=False,
+                                 scale=0.5, v_head_dim=d, distance_slopes=distance_slopes(heads), suffixes=BARE)
+    eye = torch.eye(128)
+    values = {"m.q": eye[:64], "m.k": eye[64:96], "m.v": eye[96:128], "m.o": torch.eye(128)[:, :64].contiguous(),
+              "m.q.b": torch.zeros(64), "m.k.b": torch.zeros(32), "m.v.b": torch.zeros(32)}
+    for name, param in part.all_named_params().items():
+        param.data = values[name].to(dtype).cuda()
+    part.finalize(torch.device("cuda"), dtype)
+    g = torch.Generator().manual_seed(far)
+    x = torch.randn(T, 128, generator=g)
+    x[:, 64:96] *= 0.1
+    x = x.to(torch.bfloat16).float()
+    for kv in range(kv_heads):
+        q = x[query, kv * 32:kv * 32 + 16]
+        x[far, 64 + kv * 16:64 + (kv + 1) * 16] = q / q.norm() * ((0.25 * (query - far) + 20) / (0.5 * q.norm()))
+    x = x.to(torch.bfloat16).float()
+    q, k, v = x[:, :64].reshape(T, heads, d), x[:, 64:96].reshape(T, kv_heads, d), x[:, 96:].reshape(T, kv_heads, d)
+    expected = plain.biased_attention(q, k, v, 0.5).reshape(T, 64)
+    assert (expected[query, :16] - v[far, 0]).abs().max() < 0.01        # head 0 sees nothing but the far key
+    body = lambda ctx, h, view: part.forward(ctx, h, view)
+    cuts = [70, 130, 3, 2, 60, 1, 1] + [1] * 33
+    out = harness.run_part(part, 128, dtype, body, {"a": x}, {"a": cuts}, page_size=16, num_pages=24)["a"]
+    close(out[:, :64], expected, dtype, scale=0.3)
+    assert out[:, 64:].abs().max() == 0
+
+
 def gla_part(dtype, heads, d, e, rank, tau, hidden=48, seed=2):
     from qwen_inference_lab_b200.parts import GatedLinearAttention
     from qwen_inference_lab_b200.models.virulix import BARE
