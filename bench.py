@@ -564,10 +564,7 @@ def _mixer_kernels(torch, model, sizes, pk, tokens_n, batch, context, flush, qwe
     def gla_kernel(ctx, x, view, timer):
         projected = x[:, :width].contiguous()
         mixed = torch.empty((x.shape[0], gh * ge), dtype=x.dtype, device=x.device)
-        scratch = torch.empty((x.shape[0], gh * ge), dtype=torch.float32, device=x.device) if gla._needs_scratch else None
-        timer(lambda: ops.gla_scan(projected, gla.columns, gla.decay_up.data, gla.decay_bias.data, gla.tau, gla.q_scale,
-                                   gla.norm_weight.data, gla.norm_eps, view.slots, ctx.seg_start, ctx.seg_len, ctx.seg_row,
-                                   ctx.n_segments, gh, gd, ge, mixed, scratch=scratch))
+        timer(lambda: gla.scan(ctx, projected, view, mixed))
         return mixed
     # the recurrence is float32 on the CUDA cores by the design: its prompt bound is the float32 FMA rate
     fma_peak = 148 * 128 * 2 * 1.9e9

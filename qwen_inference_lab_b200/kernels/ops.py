@@ -477,40 +477,100 @@ def gla_scan_needs_scratch(d, e) -> bool:
     return bool(code)
 
 
-def gla_scan(projected, columns, a2, a2_bias, tau, q_scale, norm_weight, eps, state, seg_start, seg_len, seg_row,
-             n_segments, n_heads, d, e, out, scratch=None):
-    """Gated linear attention over the segments of a step (see csrc/gla_scan.cu for the equations).
+GLA_WHOLE, GLA_OWN_STATE, GLA_FROM_STATE = 0, 1, 2
 
-    ``projected`` [N, width]: the stacked projection; ``columns`` = (q, k, v, g, low) first columns in it
-    (q, k: n_heads * d wide; v, g: n_heads * e; low: a2.shape[1]).  ``state`` float32 [slots, n_heads, d, e]
-    is read and written at the rows ``seg_row`` names.  ``out`` [N, n_heads * e]."""
+
+def gla_decay(projected, low_column, a2, a2_bias, tau, out=None):
+    """alpha float32 [N, channels] = sigmoid(a2 low + a2_bias)^(1/tau), ``low`` being the a2.shape[1] columns of
+    ``projected`` from ``low_column`` on: the decay of every key channel at every token, in float32."""
+    _need(projected, "projected", ndim=2); _need(a2, "a2", ndim=2); _need(a2_bias, "a2_bias", a2.dtype, 1)
+    n, ld = projected.shape
+    channels, rank = a2.shape
+    if a2_bias.shape[0] != channels or low_column + rank > ld or not tau > 0:
+        raise KernelError("gla_decay: shapes do not fit together")
+    if out is None:
+        out = torch.empty((n, channels), dtype=torch.float32, device=projected.device)
+    _need(out, "out", torch.float32, 2)
+    lib = core()
+    _check(lib, lib.qil_gla_decay(c_void_p(projected.data_ptr() + low_column * projected.element_size()), c_int(ld),
+                                  _p(a2), _p(a2_bias), c_int(rank), c_float(tau), c_int(n), c_int(channels), _p(out),
+                                  c_int(dtype_code(projected.dtype)), c_int(dtype_code(a2.dtype)), _stream()), "gla_decay")
+    return out
+
+
+def gla_scan(projected, columns, alpha, q_scale, norm_weight, eps, state, seg_start, seg_len, seg_row,
+             n_segments, n_heads, d, e, out, scratch=None, mode=GLA_WHOLE, decay_product=None):
+    """Gated linear attention over segments of a step (see csrc/gla_scan.cu for the equations).
+
+    ``projected`` [N, width]: the stacked projection; ``columns`` = (q, k, v, g) first columns in it
+    (q, k: n_heads * d wide; v, g: n_heads * e).  ``alpha`` float32 [N, n_heads * d]: the decays
+    (``gla_decay``).  ``state`` float32 [slots, n_heads, d, e] is read and written at the rows ``seg_row`` names.
+    ``out`` [N, n_heads * e].  ``scratch``: float32 [N, n_heads * e], needed when ``gla_scan_needs_scratch``: the
+    outputs then go there un-normed and ``gla_norm_gate`` finishes them.  ``mode``: GLA_WHOLE; GLA_OWN_STATE scans
+    from zero and writes only the segment's own state to ``state[seg_row]`` and the product of its decays to
+    ``decay_product`` [slots, n_heads, d]; GLA_FROM_STATE reads ``state[seg_row]``, writes the outputs and leaves
+    the state."""
     _need(projected, "projected", ndim=2); _need(out, "out", projected.dtype, 2)
-    _need(a2, "a2", ndim=2); _need(a2_bias, "a2_bias", a2.dtype, 1); _need(norm_weight, "norm_weight", a2.dtype, 1)
+    _need(alpha, "alpha", torch.float32, 2); _need(norm_weight, "norm_weight", ndim=1)
     _need(state, "state", torch.float32, 4)
     n, ld = projected.shape
-    rank = a2.shape[1]
-    q_at, k_at, v_at, g_at, low_at = (int(c) for c in columns)
-    if (a2.shape[0] != n_heads * d or a2_bias.shape[0] != n_heads * d or norm_weight.shape[0] != e
+    q_at, k_at, v_at, g_at = (int(c) for c in columns[:4])
+    if (alpha.shape != (n, n_heads * d) or norm_weight.shape[0] != e
             or tuple(state.shape[1:]) != (n_heads, d, e) or out.shape != (n, n_heads * e)):
         raise KernelError("gla_scan: shapes do not match the head counts")
-    if max(q_at + n_heads * d, k_at + n_heads * d, v_at + n_heads * e, g_at + n_heads * e, low_at + rank) > ld:
+    if max(q_at + n_heads * d, k_at + n_heads * d, v_at + n_heads * e, g_at + n_heads * e) > ld:
         raise KernelError("gla_scan: a column range lies outside the projection")
     for t in (seg_start, seg_len, seg_row):
         _need(t, "segments", torch.int32, 1)
+        if t.shape[0] < n_segments:
+            raise KernelError("gla_scan: fewer segment entries than segments")
     if scratch is not None:
         _need(scratch, "scratch", torch.float32)
         if scratch.numel() < n * n_heads * e:
             raise KernelError("gla_scan: the scratch buffer is too small")
+    if mode == GLA_OWN_STATE:
+        _need(decay_product, "decay_product", torch.float32, 3)
+        if decay_product.shape != (state.shape[0], n_heads, d):
+            raise KernelError("gla_scan: decay_product must be [states, heads, d]")
     size = projected.element_size()
     base = projected.data_ptr()
     lib = core()
     _check(lib, lib.qil_gla_scan(
         c_void_p(base + q_at * size), c_void_p(base + k_at * size), c_void_p(base + v_at * size),
-        c_void_p(base + g_at * size), c_void_p(base + low_at * size), c_int(ld), _p(a2), _p(a2_bias), c_int(rank),
-        c_float(tau), c_float(q_scale), _p(norm_weight), c_float(eps), _p(state), _p(seg_start), _p(seg_len),
-        _p(seg_row), c_int(n_segments), c_int(n), c_int(n_heads), c_int(d), c_int(e), _p(scratch), _p(out),
-        c_int(dtype_code(projected.dtype)), c_int(dtype_code(a2.dtype)), _stream()), "gla_scan",
-        kernels=1 if scratch is None else 2)
+        c_void_p(base + g_at * size), _p(alpha), c_int(ld), c_float(q_scale), _p(norm_weight), c_float(eps), _p(state),
+        _p(seg_start), _p(seg_len), _p(seg_row), c_int(n_segments), c_int(n), c_int(n_heads), c_int(d), c_int(e),
+        _p(scratch), _p(out), c_int(mode), _p(decay_product), c_int(dtype_code(projected.dtype)),
+        c_int(dtype_code(norm_weight.dtype)), _stream()), "gla_scan")
+    return out
+
+
+def gla_carry(chunk_state, decay_product, slots, carry, n_carries):
+    """Walk the chunks of long segments in order: ``chunk_state`` [chunks, heads, d, e] holds every chunk's own
+    state and receives its incoming one; the state after a segment's last chunk goes to its slot.
+    ``carry`` int32 [n_carries * 3] = (slot, first chunk, chunks)."""
+    _need(chunk_state, "chunk_state", torch.float32, 4); _need(decay_product, "decay_product", torch.float32, 3)
+    _need(slots, "slots", torch.float32, 4); _need(carry, "carry", torch.int32, 1)
+    if tuple(slots.shape[1:]) != tuple(chunk_state.shape[1:]) or decay_product.shape != chunk_state.shape[:3] \
+            or carry.shape[0] < 3 * n_carries:
+        raise KernelError("gla_carry: shapes do not fit together")
+    lib = core()
+    _check(lib, lib.qil_gla_carry(_p(chunk_state), _p(decay_product), _p(slots), _p(carry), c_int(n_carries),
+                                  c_int(chunk_state.shape[1]), c_int(chunk_state.shape[2]), c_int(chunk_state.shape[3]),
+                                  _stream()), "gla_carry")
+
+
+def gla_norm_gate(scratch, projected, gate_column, norm_weight, eps, n_heads, e, out):
+    """out = rmsnorm over each head's e values of ``scratch`` (weight ``norm_weight``) * silu(gate), the gate
+    being the columns of ``projected`` from ``gate_column`` on."""
+    _need(scratch, "scratch", torch.float32); _need(projected, "projected", ndim=2); _need(out, "out", projected.dtype, 2)
+    n = projected.shape[0]
+    if out.shape != (n, n_heads * e) or scratch.numel() < n * n_heads * e or gate_column + n_heads * e > projected.shape[1]:
+        raise KernelError("gla_norm_gate: shapes do not fit together")
+    lib = core()
+    _check(lib, lib.qil_gla_norm_gate(_p(scratch), c_void_p(projected.data_ptr() + gate_column * projected.element_size()),
+                                      c_int(projected.shape[1]), _p(norm_weight), c_float(eps), c_int(n), c_int(n_heads),
+                                      c_int(e), _p(out), c_int(dtype_code(projected.dtype)),
+                                      c_int(dtype_code(norm_weight.dtype)), _stream()), "gla_norm_gate")
     return out
 
 

@@ -7,18 +7,52 @@ Per head, with d key channels and e value channels, for the tokens of a sequence
     o_t = S_t^T (q_t * q_scale)
     y_t = W_o ( rmsnorm_e(o_t; w) * silu(W_g x_t) )  the norm is over a head's e values, w shared by heads
 
-q, k, v, the gate and the low-rank input of the decay are one stacked product; the recurrence, the norm
-and the gate are one kernel that walks every segment of the step from the request's state slot
-(``kernels.ops.gla_scan``), so prompt portions of any length and single decoded tokens take the same path
-and the result does not depend on the cut.
+q, k, v, the gate and the low-rank input of the decay are one stacked product; the decays are a small kernel
+of their own (``kernels.ops.gla_decay``); the recurrence, the norm and the gate are one kernel that walks a segment of the step from the request's state slot
+(``kernels.ops.gla_scan``): single decoded tokens and prompt portions of up to ``LONG_SEGMENT`` tokens take it
+token by token, and their result does not depend on the cut to the last bit.  Longer portions are cut into
+chunks of ``CHUNK`` tokens that run side by side: every chunk's own state from zero, a carry over the chunks
+in order, then every chunk again from its incoming state (twice the arithmetic, all chunks at once; the
+carry rounds differently from the token-by-token scan, in the last bits).
 """
 from __future__ import annotations
 
 import torch
 
+import numpy as np
+
 from ..kernels import ops
-from .base import Mixer, Param, StateSpec
+from .base import Mixer, Param, StateSpec, StepPlanner
 from .linear import Linear, StackedLinear
+
+CHUNK = 64              # tokens of a chunk of a long segment
+LONG_SEGMENT = 128      # segments longer than this are cut into chunks
+
+
+class ScanPlanner(StepPlanner):
+    """A step's segments as the scan wants them: the short ones as they are (first token, tokens, state slot),
+    the long ones as chunks (first token, tokens, index among the step's chunks) and one carry entry per long
+    segment (state slot, first chunk, chunks).  All recurrent layers of a model share the plan."""
+    key = "state_scan"
+
+    def plan(self, segments):
+        lens = np.asarray(segments.lens)
+        short = np.nonzero(lens <= LONG_SEGMENT)[0]
+        chunks, carry = [], []
+        for i in np.nonzero(lens > LONG_SEGMENT)[0]:
+            first, count = int(segments.first[i]), int(lens[i])
+            carry.append((int(segments.rows[i]), len(chunks), -(-count // CHUNK)))
+            chunks += [(first + off, min(CHUNK, count - off), len(chunks) + off // CHUNK) for off in range(0, count, CHUNK)]
+        chunks = np.array(chunks, dtype=np.int64).reshape(-1, 3)
+        return dict(short_start=segments.first[short], short_len=lens[short], short_row=np.asarray(segments.rows)[short],
+                    chunk_start=chunks[:, 0], chunk_len=chunks[:, 1], chunk_index=chunks[:, 2],
+                    carry=np.array(carry, dtype=np.int64).reshape(-1))
+
+    def refresh_single_tokens(self, arrays, segments):
+        return True         # single tokens in the same rows: nothing here depends on their positions
+
+
+_PLANNER = ScanPlanner()
 
 
 class GatedLinearAttention(Mixer):
@@ -63,17 +97,38 @@ class GatedLinearAttention(Mixer):
     def cache_spec(self):
         return StateSpec((self.n_heads, self.key_dim, self.value_dim), torch.float32)
 
+    def step_planners(self):
+        return {**super().step_planners(), _PLANNER.key: _PLANNER}
+
     takes_norm = True
 
     def forward(self, ctx, x, cache, residual=None, norm=None):
         """x [N, hidden] -> [N, hidden] (+ residual); ``cache`` is a StateView with one slot per request row."""
-        n = x.shape[0]
         projected = self.projection.forward(ctx, x, norm=norm)
-        mixed = ctx.empty((n, self.n_heads * self.value_dim))
-        scratch = None
-        if self._needs_scratch:
-            scratch = ctx.empty((n, self.n_heads * self.value_dim), dtype=torch.float32)
-        ops.gla_scan(projected, self.columns, self.decay_up.data, self.decay_bias.data, self.tau, self.q_scale,
-                     self.norm_weight.data, self.norm_eps, cache.slots, ctx.seg_start, ctx.seg_len, ctx.seg_row,
-                     ctx.n_segments, self.n_heads, self.key_dim, self.value_dim, mixed, scratch=scratch)
+        mixed = ctx.empty((x.shape[0], self.n_heads * self.value_dim))
+        self.scan(ctx, projected, cache, mixed)
         return self.out.forward(ctx, mixed, residual=residual)
+
+    def scan(self, ctx, projected, cache, mixed):
+        """The recurrence, the norm and the gate over the step's segments: ``projected`` -> ``mixed``."""
+        n = projected.shape[0]
+        plan = ctx.plans[_PLANNER.key]
+        scratch = ctx.empty((n, self.n_heads * self.value_dim), dtype=torch.float32) if self._needs_scratch else None
+        alpha = ops.gla_decay(projected, self.columns[4], self.decay_up.data, self.decay_bias.data, self.tau)
+        common = (projected, self.columns, alpha, self.q_scale, self.norm_weight.data, self.norm_eps)
+        sizes = (self.n_heads, self.key_dim, self.value_dim, mixed)
+        n_short, n_chunks = plan.count["short_start"], plan.count["chunk_start"]
+        if n_short:
+            ops.gla_scan(*common, cache.slots, plan.array["short_start"], plan.array["short_len"],
+                         plan.array["short_row"], n_short, *sizes, scratch=scratch)
+        if n_chunks:
+            chunk = (plan.array["chunk_start"], plan.array["chunk_len"], plan.array["chunk_index"], n_chunks)
+            states = ctx.empty((n_chunks, self.n_heads, self.key_dim, self.value_dim), dtype=torch.float32)
+            decays = ctx.empty((n_chunks, self.n_heads, self.key_dim), dtype=torch.float32)
+            ops.gla_scan(*common, states, *chunk, *sizes, mode=ops.GLA_OWN_STATE, decay_product=decays)
+            ops.gla_carry(states, decays, cache.slots, plan.array["carry"], plan.count["carry"] // 3)
+            ops.gla_scan(*common, states, *chunk, *sizes, scratch=scratch, mode=ops.GLA_FROM_STATE)
+        if scratch is not None:
+            ops.gla_norm_gate(scratch, projected, self.columns[3], self.norm_weight.data, self.norm_eps, self.n_heads,
+                              self.value_dim, mixed)
+        return mixed

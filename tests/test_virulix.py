@@ -99,3 +99,22 @@ def test_plain_router_weights_are_a_softmax_over_the_chosen_alone():
     chosen, weights = plain.route(torch.tensor([[3.0, 1.0, 2.0, -5.0]]), w, "r.", 2)
     assert chosen.tolist() == [[0, 2]]
     torch.testing.assert_close(weights, torch.softmax(torch.tensor([[3.0, 2.0]]), dim=-1))
+
+
+def test_scan_planner_cuts_long_segments_into_chunks():
+    import numpy as np
+    from qwen_inference_lab_b200.parts import Segments
+    from qwen_inference_lab_b200.parts.linear_attention import CHUNK, LONG_SEGMENT, ScanPlanner
+    lens = np.array([1, LONG_SEGMENT, LONG_SEGMENT + 1, 7, 3 * CHUNK])
+    first = np.concatenate(([0], np.cumsum(lens[:-1])))
+    plan = ScanPlanner().plan(Segments(rows=np.array([3, 0, 2, 1, 5]), first=first, lens=lens,
+                                       starts=np.array([9, 0, 40, 0, 1000]), n_tokens=int(lens.sum())))
+    assert plan["short_start"].tolist() == [0, 1, 1 + LONG_SEGMENT + LONG_SEGMENT + 1]
+    assert plan["short_len"].tolist() == [1, LONG_SEGMENT, 7] and plan["short_row"].tolist() == [3, 0, 1]
+    assert plan["chunk_len"].tolist() == [CHUNK, CHUNK, 1, CHUNK, CHUNK, CHUNK]
+    assert plan["chunk_index"].tolist() == list(range(6))
+    assert plan["chunk_start"].tolist()[:3] == [129, 129 + CHUNK, 129 + 2 * CHUNK]
+    assert plan["carry"].tolist() == [2, 0, 3, 5, 3, 3]
+    singles = ScanPlanner().plan(Segments(rows=np.arange(4), first=np.arange(4), lens=np.ones(4, dtype=np.int64),
+                                          starts=np.array([5, 6, 7, 8]), n_tokens=4))
+    assert singles["chunk_start"].size == 0 and singles["carry"].size == 0 and singles["short_len"].tolist() == [1] * 4
