@@ -38,6 +38,9 @@ __device__ __forceinline__ float decay_from_logit(float z, float inv_tau) {
 
 #define GLA_R 32          // rows of a column that one thread holds
 #define GLA_THREADS 256
+#ifndef GLA_MIN_BLOCKS
+#define GLA_MIN_BLOCKS 2  // blocks per multiprocessor the scan is compiled for
+#endif
 
 // alpha[t, c] = sigmoid(b_c + sum_j A2[c, j] low[t, j])^(1/tau) for every token and key channel: float32, once
 // per layer and step (the scan's blocks all read it).
@@ -83,7 +86,7 @@ __device__ __forceinline__ void gla_norm_gate_rows(const float* o_rows, int o_st
 #define GLA_FROM_STATE 2   // from the given state, outputs, nothing written back
 
 template <typename T, typename W, bool FUSED, int MODE>
-__global__ void __launch_bounds__(GLA_THREADS)
+__global__ void __launch_bounds__(GLA_THREADS, GLA_MIN_BLOCKS)
 gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v, const T* __restrict__ g,
                 const float* __restrict__ alpha, int ld, float q_scale, const W* __restrict__ norm_w, float eps,
                 float* __restrict__ state, float* __restrict__ decay_product, const int* __restrict__ seg_start,
@@ -91,10 +94,13 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
                 int ds_count, int tile_cols, float* __restrict__ o_raw, T* __restrict__ out) {
     constexpr int R = GLA_R;
     extern __shared__ float smem[];
-    float* sq = smem;                    // [TB][d]
-    float* sk = sq + GLA_TB * d;         // [TB][d]
-    float* sa = sk + GLA_TB * d;         // [TB][d]
-    float* sv = sa + GLA_TB * d;         // [TB][tile_cols]
+    // q, k and the decays of a token: ds_count blocks of R values, each followed by four unused floats, so that
+    // the threads of a quarter warp (which differ in their block) read their 16-byte pieces from different banks
+    const int stride = ds_count * (R + 4);
+    float* sq = smem;                    // [TB][stride]
+    float* sk = sq + GLA_TB * stride;    // [TB][stride]
+    float* sa = sk + GLA_TB * stride;    // [TB][stride]
+    float* sv = sa + GLA_TB * stride;    // [TB][tile_cols]
     float* so = sv + GLA_TB * tile_cols; // [TB][tile_cols]
     float* sp = so + GLA_TB * tile_cols; // [d]: the product of the decays so far (GLA_OWN_STATE)
     qil_wait_for_producer();
@@ -107,10 +113,10 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     const bool owner = local < tile_cols && col < e;
     float* slot = state + ((size_t)row * n_heads + head) * d * e;
 
-    float S[R];
+    float S[R];           // rows ds * R .. ds * R + R - 1 of the column (rows past d stay zero)
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int dd = r * ds_count + ds;
+        const int dd = ds * R + r;
         S[r] = (MODE != GLA_OWN_STATE && owner && dd < d) ? slot[(size_t)dd * e + col] : 0.f;
     }
     if (MODE == GLA_OWN_STATE)
@@ -119,12 +125,14 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     for (int t0 = 0; t0 < count; t0 += GLA_TB) {
         const int nb = count - t0 < GLA_TB ? count - t0 : GLA_TB;
         __syncthreads();
-        for (int i = tid; i < nb * d; i += threads) {
-            const int tb = i / d, dd = i % d;
+        for (int i = tid; i < nb * ds_count * R; i += threads) {
+            const int tb = i / (ds_count * R), dd = i % (ds_count * R);
+            const int to = tb * stride + (dd / R) * (R + 4) + dd % R;
+            const bool real = dd < d;           // rows past d: zeros, which keep their (zero) state rows zero
             const size_t at = (size_t)(first + t0 + tb) * ld + head * d + dd;
-            if (MODE != GLA_OWN_STATE) sq[tb * d + dd] = to_f32<T>(q[at]) * q_scale;
-            sk[tb * d + dd] = to_f32<T>(k[at]);
-            sa[tb * d + dd] = alpha[(size_t)(first + t0 + tb) * n_heads * d + head * d + dd];
+            if (MODE != GLA_OWN_STATE) sq[to] = real ? to_f32<T>(q[at]) * q_scale : 0.f;
+            sk[to] = real ? to_f32<T>(k[at]) : 0.f;
+            sa[to] = real ? alpha[(size_t)(first + t0 + tb) * n_heads * d + head * d + dd] : 0.f;
         }
         for (int i = tid; i < nb * tile_cols; i += threads) {
             const int tb = i / tile_cols, c = col0 + i % tile_cols;
@@ -134,19 +142,29 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
         if (MODE == GLA_OWN_STATE) {
             for (int dd = tid; dd < d; dd += threads) {       // the same thread every batch: no barrier needed
                 float product = sp[dd];
-                for (int tb = 0; tb < nb; ++tb) product *= sa[tb * d + dd];
+                for (int tb = 0; tb < nb; ++tb) product *= sa[tb * stride + (dd / R) * (R + 4) + dd % R];
                 sp[dd] = product;
             }
         }
         for (int tb = 0; tb < nb; ++tb) {
             const float vc = owner ? sv[tb * tile_cols + local] : 0.f;
             float o = 0.f;
+            const float4* a4 = reinterpret_cast<const float4*>(sa + tb * stride + ds * (R + 4));
+            const float4* k4 = reinterpret_cast<const float4*>(sk + tb * stride + ds * (R + 4));
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tb * stride + ds * (R + 4));
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int dd = r * ds_count + ds;
-                if (dd < d) {
-                    S[r] = fmaf(sa[tb * d + dd], S[r], sk[tb * d + dd] * vc);
-                    if (MODE != GLA_OWN_STATE) o = fmaf(S[r], sq[tb * d + dd], o);
+            for (int r4 = 0; r4 < R / 4; ++r4) {
+                const float4 a = a4[r4], kk = k4[r4];
+                S[4 * r4 + 0] = fmaf(a.x, S[4 * r4 + 0], kk.x * vc);
+                S[4 * r4 + 1] = fmaf(a.y, S[4 * r4 + 1], kk.y * vc);
+                S[4 * r4 + 2] = fmaf(a.z, S[4 * r4 + 2], kk.z * vc);
+                S[4 * r4 + 3] = fmaf(a.w, S[4 * r4 + 3], kk.w * vc);
+                if (MODE != GLA_OWN_STATE) {
+                    const float4 qq = q4[r4];
+                    o = fmaf(S[4 * r4 + 0], qq.x, o);
+                    o = fmaf(S[4 * r4 + 1], qq.y, o);
+                    o = fmaf(S[4 * r4 + 2], qq.z, o);
+                    o = fmaf(S[4 * r4 + 3], qq.w, o);
                 }
             }
             if (MODE == GLA_OWN_STATE) continue;
@@ -165,7 +183,7 @@ gla_scan_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __res
     if (MODE == GLA_FROM_STATE) return;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int dd = r * ds_count + ds;
+        const int dd = ds * R + r;
         if (owner && dd < d) slot[(size_t)dd * e + col] = S[r];
     }
     if (MODE == GLA_OWN_STATE && col0 == 0)
@@ -251,7 +269,7 @@ extern "C" int qil_gla_scan(const void* q, const void* k, const void* v, const v
     const bool fused = tiles == 1;
     if (!fused && o_raw == nullptr && mode != GLA_OWN_STATE) QIL_REFUSE("gla_scan: %d value columns per head need the scratch buffer", e);
     const int threads = (tile_cols * ds_count + 31) / 32 * 32;
-    const size_t smem = ((size_t)GLA_TB * (3 * d + 2 * tile_cols) + d) * sizeof(float);
+    const size_t smem = ((size_t)GLA_TB * (3 * ds_count * (GLA_R + 4) + 2 * tile_cols) + d) * sizeof(float);
     dim3 grid(n_heads * tiles, n_segments);
     cudaError_t err = cudaSuccess;
 #define QIL_GLA_GO(F, M)                                                                                         \
