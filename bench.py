@@ -465,15 +465,17 @@ class _ModelBench:
         one = lambda i: runner.run([StepEntry(rid, [tokens[i][rid]], [0]) for rid in range(batch)])
         for i in range(warmup):
             one(i)
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # every step between its own pair of events, the median of them: a step that waits for the allocator
+        # (a new graph pool, a library's workspace) does not count for sixteen
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         torch.cuda.synchronize()
-        start.record()
+        marks[0].record()
         for i in range(warmup, warmup + steps):
             logits = one(i)
-        stop.record()
+            marks[i - warmup + 1].record()
         torch.cuda.synchronize()
         assert torch.isfinite(logits).all()
-        return start.elapsed_time(stop) / steps
+        return statistics.median(a.elapsed_time(b) for a, b in zip(marks, marks[1:]))
 
 
 def _mixer_kernels(torch, model, sizes, pk, tokens_n, batch, context, flush, qwen):
@@ -615,7 +617,7 @@ def run_virulix(args):
                 ms = bench.prefill(tokens_n, flush)
                 entry[f"prefill_{tokens_n}"] = {"ms": round(ms, 3), "tokens_per_s": round(tokens_n / ms * 1e3, 1)}
             for batch, context in ((1, 2048), (8, 2048), (32, 2048)):
-                ms = bench.decode(batch, context, args.steps, args.warmup)
+                ms = bench.decode(batch, context, args.steps, max(args.warmup, 6))
                 entry[f"decode_b{batch}_c{context}"] = {"ms": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1)}
             result["models"][label] = entry
         for kernel, ms, frac, of in _mixer_kernels(torch, virulix, sizes, pk, 2048, 8, 2048, flush, qwen):

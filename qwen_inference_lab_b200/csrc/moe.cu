@@ -19,7 +19,8 @@
 // The activation is the clamped swish of gated_activation.cu (kind 2) or silu (kind 0).
 #include "common.cuh"
 
-#define MOE_BM 64
+#define MOE_BM 128         // rows of a tile of the list (the float32 kernel takes it as two halves of MOE_FM)
+#define MOE_FM 64
 #define MOE_BN 64
 #define MOE_BK 16
 #define MOE_MAX_EXPERTS 1024
@@ -197,18 +198,21 @@ moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w
                        const int* __restrict__ sorted_pairs, int top, const float* __restrict__ pair_weight,
                        T* __restrict__ hidden, float* __restrict__ y, int n_out, int K, int kind, float limit,
                        float alpha) {
-    __shared__ float As[MOE_BK][MOE_BM + 4];
+    __shared__ float As[MOE_BK][MOE_FM + 4];
     __shared__ float W0s[MOE_BK][MOE_BN + 4];
     __shared__ float W1s[DUAL ? MOE_BK : 1][MOE_BN + 4];
-    __shared__ int src_row[MOE_BM];
+    __shared__ int src_row[MOE_FM];
     qil_wait_for_producer();
     qil_release_consumer();
     const int tile = blockIdx.y;
     if (tile >= info[0]) return;
-    const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
+    // blockIdx.z: which half of the tile's rows
+    const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1] + MOE_FM * blockIdx.z;
+    const int rows = min(MOE_FM, tiles[3 * tile + 2] - MOE_FM * (int)blockIdx.z);
+    if (rows <= 0) return;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int n0 = blockIdx.x * MOE_BN;
-    if (tid < MOE_BM) src_row[tid] = tid < rows ? (DUAL ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
+    if (tid < MOE_FM) src_row[tid] = tid < rows ? (DUAL ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
     __syncthreads();
     const W* e0 = w0 + (size_t)expert * n_out * K;
     const W* e1 = DUAL ? w1 + (size_t)expert * n_out * K : nullptr;
@@ -274,10 +278,11 @@ moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w
 }
 
 // ------------------------------------------------------------------ the same products on the tensor cores
-// bfloat16 rows and weights, float32 accumulators (mma.sync m16n8k16).  A block takes the same 64-row tile of
-// one expert and 64 output features; its four warps own 16 rows each.  Rows and weights move through two
-// stages of 32 k-values with cp.async; rows past the tile's end and k-values past K arrive as zeros.
-#define MOE_TK 32
+// bfloat16 rows and weights, float32 accumulators (mma.sync m16n8k16).  A block takes a 128-row tile of one expert
+// and 64 output features (of the gate and of the up matrix at once); its eight warps own 32 x 32 corners.
+// Rows and weights move through a ring of three stages of 64 k-values with cp.async; rows past the tile's end and k-values past K arrive as zeros.
+#define MOE_TK 64
+#define MOE_STAGES 3
 #define MOE_LDS (MOE_TK + 8)       // row stride in elements: rows start 16 bytes apart mod 128
 
 __device__ __forceinline__ void moe_cp_async16(void* smem, const void* gmem, bool valid) {
@@ -297,15 +302,18 @@ __device__ __forceinline__ void moe_mma_bf16(float (&c)[4], const unsigned (&a)[
 }
 
 template <bool DUAL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
                       const int* __restrict__ tiles, const int* __restrict__ info,
                       const int* __restrict__ sorted_pairs, int top, const float* __restrict__ pair_weight,
                       bf16* __restrict__ hidden, float* __restrict__ y, int n_out, int K, int kind, float limit,
                       float alpha) {
-    __shared__ __align__(16) bf16 sA[2][MOE_BM][MOE_LDS];
-    __shared__ __align__(16) bf16 sB0[2][MOE_BN][MOE_LDS];
-    __shared__ __align__(16) bf16 sB1[DUAL ? 2 : 1][DUAL ? MOE_BN : 1][MOE_LDS];
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    typedef bf16 (*TileA)[MOE_BM][MOE_LDS];
+    typedef bf16 (*TileB)[MOE_BN][MOE_LDS];
+    TileA sA = reinterpret_cast<TileA>(moe_smem);                                   // [stages][128][LDS]
+    TileB sB0 = reinterpret_cast<TileB>(moe_smem + sizeof(bf16) * MOE_STAGES * MOE_BM * MOE_LDS);
+    TileB sB1 = sB0 + MOE_STAGES;                                                   // only with DUAL
     __shared__ int src_row[MOE_BM];
     qil_wait_for_producer();
     qil_release_consumer();
@@ -313,6 +321,7 @@ moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restric
     if (tile >= info[0]) return;
     const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;      // this warp's 32 x 32 corner of the 128 x 64 tile
     const int n0 = blockIdx.x * MOE_BN;
     if (tid < MOE_BM) src_row[tid] = tid < rows ? (DUAL ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
     __syncthreads();
@@ -320,77 +329,112 @@ moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restric
     const bf16* e1 = DUAL ? w1 + (size_t)expert * n_out * K : nullptr;
 
     auto issue = [&](int stage, int k0) {
-        // 64 rows x 4 pieces of 16 bytes per operand: two pieces a thread
+        // 16-byte pieces: 128 rows x 8 of A (four a thread), 64 rows x 8 of every weight tile (two a thread)
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * 256;
+            const int r = idx >> 3, piece = idx & 7, k = k0 + piece * 8;
+            const bool a_ok = k < K && src_row[r] >= 0;
+            moe_cp_async16(&sA[stage][r][piece * 8], A + (a_ok ? (size_t)src_row[r] * lda + k : 0), a_ok);
+        }
 #pragma unroll
         for (int it = 0; it < 2; ++it) {
-            const int idx = tid + it * 128;
-            const int r = idx >> 2, piece = idx & 3, k = k0 + piece * 8;
-            const bool in_k = k < K;
-            const bool a_ok = in_k && src_row[r] >= 0;
-            moe_cp_async16(&sA[stage][r][piece * 8], A + (a_ok ? (size_t)src_row[r] * lda + k : 0), a_ok);
-            const bool b_ok = in_k && n0 + r < n_out;
+            const int idx = tid + it * 256;
+            const int r = idx >> 3, piece = idx & 7, k = k0 + piece * 8;
+            const bool b_ok = k < K && n0 + r < n_out;
             moe_cp_async16(&sB0[stage][r][piece * 8], e0 + (b_ok ? (size_t)(n0 + r) * K + k : 0), b_ok);
             if (DUAL) moe_cp_async16(&sB1[stage][r][piece * 8], e1 + (b_ok ? (size_t)(n0 + r) * K + k : 0), b_ok);
         }
     };
-    float acc0[MOE_BN / 8][4], acc1[DUAL ? MOE_BN / 8 : 1][4];
+    float acc0[2][4][4], acc1[DUAL ? 2 : 1][4][4];
 #pragma unroll
-    for (int i = 0; i < MOE_BN / 8; ++i) { acc0[i][0] = acc0[i][1] = acc0[i][2] = acc0[i][3] = 0.f; }
+    for (int m = 0; m < 2; ++m)
 #pragma unroll
-    for (int i = 0; i < (DUAL ? MOE_BN / 8 : 1); ++i) { acc1[i][0] = acc1[i][1] = acc1[i][2] = acc1[i][3] = 0.f; }
+        for (int n = 0; n < 4; ++n) {
+            acc0[m][n][0] = acc0[m][n][1] = acc0[m][n][2] = acc0[m][n][3] = 0.f;
+            if (DUAL) acc1[m][n][0] = acc1[m][n][1] = acc1[m][n][2] = acc1[m][n][3] = 0.f;
+        }
 
+    // a ring of MOE_STAGES stages: the copies of the next two steps are under way while one is multiplied
     const int steps = (K + MOE_TK - 1) / MOE_TK;
-    issue(0, 0);
-    asm volatile("cp.async.commit_group;\n" ::);
-    for (int step = 0; step < steps; ++step) {
-        const int stage = step & 1;
-        if (step + 1 < steps) issue(stage ^ 1, (step + 1) * MOE_TK);
+#pragma unroll
+    for (int ahead = 0; ahead < MOE_STAGES - 1; ++ahead) {
+        if (ahead < steps) issue(ahead, ahead * MOE_TK);
         asm volatile("cp.async.commit_group;\n" ::);
-        asm volatile("cp.async.wait_group 1;\n" ::);
-        __syncthreads();
+    }
+    for (int step = 0; step < steps; ++step) {
+        const int stage = step % MOE_STAGES;
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(MOE_STAGES - 2));
+        __syncthreads();        // this step's stage has landed for everyone, and everyone is done with the stage refilled next
+        if (step + MOE_STAGES - 1 < steps) issue((step + MOE_STAGES - 1) % MOE_STAGES, (step + MOE_STAGES - 1) * MOE_TK);
+        asm volatile("cp.async.commit_group;\n" ::);
+        if (wm >= rows) continue;      // a tile of few rows (single tokens): warps past them only copy
 #pragma unroll
         for (int ks = 0; ks < MOE_TK / 16; ++ks) {
-            unsigned a[4];
-            moe_ldmatrix_x4(a[0], a[1], a[2], a[3],
-                            &sA[stage][warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)][ks * 16 + (lane >> 4) * 8]);
+            unsigned a[2][4];
 #pragma unroll
-            for (int np = 0; np < MOE_BN / 16; ++np) {
+            for (int m = 0; m < 2; ++m)
+                moe_ldmatrix_x4(a[m][0], a[m][1], a[m][2], a[m][3],
+                                &sA[stage][wm + m * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
                 unsigned b0, b1, b2, b3;
                 moe_ldmatrix_x4(b0, b1, b2, b3,
-                                &sB0[stage][np * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
-                moe_mma_bf16(acc0[2 * np], a, b0, b1);
-                moe_mma_bf16(acc0[2 * np + 1], a, b2, b3);
+                                &sB0[stage][wn + np * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+                for (int m = 0; m < 2; ++m) {
+                    moe_mma_bf16(acc0[m][2 * np], a[m], b0, b1);
+                    moe_mma_bf16(acc0[m][2 * np + 1], a[m], b2, b3);
+                }
                 if (DUAL) {
                     moe_ldmatrix_x4(b0, b1, b2, b3,
-                                    &sB1[stage][np * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
-                    moe_mma_bf16(acc1[2 * np], a, b0, b1);
-                    moe_mma_bf16(acc1[2 * np + 1], a, b2, b3);
-                }
-            }
-        }
-        __syncthreads();
-    }
+                                    &sB1[stage][wn + np * 16 + (lane >> 4) * 8 + (lane & 7)][ks * 16 + ((lane >> 3) & 1) * 8]);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = warp * 16 + (lane >> 2) + half * 8;
-        if (r >= rows) continue;
-        const int pair = DUAL ? 0 : sorted_pairs[row0 + r];
-        const float scale = DUAL ? 1.f : pair_weight[pair];
-#pragma unroll
-        for (int nt = 0; nt < MOE_BN / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int n = n0 + nt * 8 + (lane & 3) * 2 + e;
-                if (n >= n_out) continue;
-                if (DUAL) {
-                    const float g = round_to<bf16>(acc0[nt][half * 2 + e]), u = round_to<bf16>(acc1[nt][half * 2 + e]);
-                    hidden[(size_t)(row0 + r) * n_out + n] = __float2bfloat16_rn(expert_activation(kind, g, u, limit, alpha));
-                } else {
-                    y[(size_t)pair * n_out + n] = scale * acc0[nt][half * 2 + e];
+                    for (int m = 0; m < 2; ++m) {
+                        moe_mma_bf16(acc1[m][2 * np], a[m], b0, b1);
+                        moe_mma_bf16(acc1[m][2 * np + 1], a[m], b2, b3);
+                    }
                 }
             }
         }
     }
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm + m * 16 + (lane >> 2) + half * 8;
+            if (r >= rows) continue;
+            const int pair = DUAL ? 0 : sorted_pairs[row0 + r];
+            const float scale = DUAL ? 1.f : pair_weight[pair];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int n = n0 + wn + nt * 8 + (lane & 3) * 2 + e;
+                    if (n >= n_out) continue;
+                    if (DUAL) {
+                        const float g = round_to<bf16>(acc0[m][nt][half * 2 + e]), u = round_to<bf16>(acc1[m][nt][half * 2 + e]);
+                        hidden[(size_t)(row0 + r) * n_out + n] = __float2bfloat16_rn(expert_activation(kind, g, u, limit, alpha));
+                    } else {
+                        y[(size_t)pair * n_out + n] = scale * acc0[m][nt][half * 2 + e];
+                    }
+                }
+            }
+        }
+    }
+}
+
+static int moe_mma_smem(bool dual) {
+    return (int)sizeof(bf16) * MOE_STAGES * (MOE_BM + (dual ? 2 : 1) * MOE_BN) * MOE_LDS;
+}
+static int moe_mma_configure() {
+    static bool configured = false;
+    if (configured) return 0;
+    cudaError_t a = cudaFuncSetAttribute(moe_expert_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_mma_smem(true));
+    cudaError_t b = cudaFuncSetAttribute(moe_expert_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_mma_smem(false));
+    if (a != cudaSuccess || b != cudaSuccess) QIL_REFUSE("moe: cannot reserve %d bytes of shared memory", moe_mma_smem(true));
+    configured = true;
+    return 0;
 }
 
 static bool moe_tensor_cores_usable(int act_dtype, int weight_dtype, int lda, int K, const void* a, const void* b,
@@ -455,11 +499,13 @@ extern "C" int qil_moe_gate_up(const void* x, int lda, const void* gate_w, const
     if (max_tiles > 65535) QIL_REFUSE("moe_gate_up: %d row tiles are too many for one launch", max_tiles);
     dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
     if (moe_tensor_cores_usable(act_dtype, weight_dtype, lda, K, x, gate_w, up_w)) {
-        qil_launch_chained(moe_expert_mma_kernel<true>, grid, dim3(128), 0, stream, (const bf16*)x, lda,
+        if (moe_mma_configure()) return -1;
+        qil_launch_chained(moe_expert_mma_kernel<true>, grid, dim3(256), moe_mma_smem(true), stream, (const bf16*)x, lda,
                            (const bf16*)gate_w, (const bf16*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
                            (bf16*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha);
         QIL_CHECK_LAUNCH();
     }
+    grid.z = MOE_BM / MOE_FM;
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         (qil_launch_chained(moe_expert_gemm_kernel<T, W, true>, grid, dim3(256), 0, stream, (const T*)x, lda,
                             (const W*)gate_w, (const W*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
@@ -474,11 +520,13 @@ extern "C" int qil_moe_down(const void* hidden, const void* down_w, const int* t
     if (max_tiles > 65535) QIL_REFUSE("moe_down: %d row tiles are too many for one launch", max_tiles);
     dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
     if (moe_tensor_cores_usable(act_dtype, weight_dtype, K, K, hidden, down_w, down_w)) {
-        qil_launch_chained(moe_expert_mma_kernel<false>, grid, dim3(128), 0, stream, (const bf16*)hidden, K,
+        if (moe_mma_configure()) return -1;
+        qil_launch_chained(moe_expert_mma_kernel<false>, grid, dim3(256), moe_mma_smem(false), stream, (const bf16*)hidden, K,
                            (const bf16*)down_w, (const bf16*)nullptr, tiles, info, sorted_pairs, 1, pair_weight,
                            (bf16*)nullptr, y, n_out, K, 0, 0.f, 0.f);
         QIL_CHECK_LAUNCH();
     }
+    grid.z = MOE_BM / MOE_FM;
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         (qil_launch_chained(moe_expert_gemm_kernel<T, W, false>, grid, dim3(256), 0, stream, (const T*)hidden, K,
                             (const W*)down_w, (const W*)nullptr, tiles, info, sorted_pairs, 1, pair_weight,
