@@ -169,6 +169,8 @@ struct AtParams {
     int table_stride;
     int n_q_heads, n_kv_heads, page_size;
     float scale_log2;
+    // null, or one slope per query head times log2(e): score = q.k * scale - slope_h * (query position - key position)
+    const float* slopes_log2;
     int* error_word;
     long long* trace;           // only read when compiled with AT_TRACE
 };
@@ -345,6 +347,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int row = quarter * 32 + lane;                 // query row of this thread = its TMEM lane
         const int pos = pos0 + row;
         const unsigned lane_base = (unsigned)(quarter * 32) << 16;
+        // With a distance bias the scores are scaled and biased first and the steps below take them as they are.
+        const bool biased = p.slopes_log2 != nullptr;
+        const float slope = biased ? p.slopes_log2[head] : 0.f;
+        const float scale_later = biased ? 1.0f : p.scale_log2;
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -370,6 +376,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             // with the subtraction, inside the exponent.  Four running maxima and four running sums: one
             // chain of 64 dependent operations would cost this warp, alone on its scheduler, their latency.
             const int key0 = j * AT_N;
+            if (biased) {
+                const float base = slope * (float)(key0 - pos);
+#pragma unroll
+                for (int i = 0; i < AT_N; ++i) s[i] = fmaf(s[i], p.scale_log2, fmaf(slope, (float)i, base));
+            }
             if (key0 + AT_N - 1 > pos0) {
 #pragma unroll
                 for (int i = 0; i < AT_N; ++i) s[i] = (key0 + i <= pos) ? s[i] : -INFINITY;
@@ -380,7 +391,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 mx[0] = fmaxf(mx[0], s[i]); mx[1] = fmaxf(mx[1], s[i + 1]);
                 mx[2] = fmaxf(mx[2], s[i + 2]); mx[3] = fmaxf(mx[3], s[i + 3]);
             }
-            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_later;
             // Move the maximum only when it grew by more than 2^8: until then exp2(s - m_used) <= 256,
             // harmless in float32 and bfloat16, and O needs no rescale (which costs a TMEM round trip).
             const bool grow = tmax > m_used + 8.0f;            // also true at the first tile (m_used = -inf)
@@ -395,7 +406,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 float e[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    e[i] = at_exp2(fmaf(s[c * 8 + i], p.scale_log2, minus_m));
+                    e[i] = at_exp2(fmaf(s[c * 8 + i], scale_later, minus_m));
                     sums[i & 3] += e[i];
                 }
                 __nv_bfloat162 b0 = __floats2bfloat162_rn(e[0], e[1]), b1 = __floats2bfloat162_rn(e[2], e[3]);
@@ -509,10 +520,12 @@ extern "C" int qil_attn_tc_keys_per_tile() { return AT_N; }
 // tile_info int32 [n_tiles, 4] = (first token, its absolute position, 128, block-table row): whole tiles only.
 // page_size must divide the keys per tile and be a multiple of 8.  error_word: a device int, zeroed by the
 // caller once.  trace: null, or 3 * 1024 int64 for the time stamps of block (0, 0) in a build with AT_TRACE.
-extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
-                                   int n_tokens, const int* block_table, int table_stride, int n_q_heads,
-                                   int n_kv_heads, int page_size, int num_pages, float scale, int* error_word,
-                                   long long* trace, cudaStream_t stream) {
+// slopes_log2: null, or float32 [n_q_heads] on the device: a distance bias per query head (see AtParams).
+extern "C" int qil_attn_tc_prefill_biased(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                          int n_tokens, const int* block_table, int table_stride, int n_q_heads,
+                                          int n_kv_heads, int page_size, int num_pages, float scale,
+                                          const float* slopes_log2, int* error_word, long long* trace,
+                                          cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (n_kv_heads <= 0 || n_q_heads % n_kv_heads) QIL_REFUSE("attn_tc: %d query heads, %d kv heads", n_q_heads, n_kv_heads);
     if (page_size < 8 || page_size > AT_N || AT_N % page_size || page_size % 8)
@@ -548,6 +561,7 @@ extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, con
     p.out = (bf16*)out; p.block_table = block_table; p.table_stride = table_stride;
     p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size;
     p.scale_log2 = scale * 1.4426950408889634f;
+    p.slopes_log2 = slopes_log2;
     p.error_word = error_word;
     p.trace = trace;
     const int smem = AT_QTILE + 2 * AT_STAGES * AT_TILE + (int)sizeof(AtShared);
@@ -559,4 +573,12 @@ extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, con
     }
     attn_tc_kernel<<<dim3(n_q_heads, n_tiles), AT_THREADS, smem, stream>>>(map_q, map_kv, p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_attn_tc_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                   int n_tokens, const int* block_table, int table_stride, int n_q_heads,
+                                   int n_kv_heads, int page_size, int num_pages, float scale, int* error_word,
+                                   long long* trace, cudaStream_t stream) {
+    return qil_attn_tc_prefill_biased(q, kv, out, tile_info, n_tiles, n_tokens, block_table, table_stride, n_q_heads,
+                                      n_kv_heads, page_size, num_pages, scale, nullptr, error_word, trace, stream);
 }

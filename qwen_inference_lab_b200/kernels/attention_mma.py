@@ -267,7 +267,7 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
 
 def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, slopes_log2=None):
     """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values.
-    ``slopes_log2``: see ``prefill`` (the tensor-memory kernel has no such bias: all tiles then take the tiled one)."""
+    ``slopes_log2``: see ``prefill``."""
     if q.dtype != torch.bfloat16 or cache.pages.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
     if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
@@ -275,13 +275,13 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
     arrays, counts = step_plan(ctx)
     n_tiles, n_big, n_rest, n_decode = (counts[name] // 4 for name in
                                         ("tile_info", "big_tile_info", "rest_tile_info", "decode_info"))
-    if n_big and slopes_log2 is None and attention_tc.supports(head_dim, cache.page_size, window):
+    if n_big and attention_tc.supports(head_dim, cache.page_size, window):
         # whole 128-token tiles on tcgen05 with the accumulators in tensor memory, the leftovers below
         attention_tc.prefill(q, cache.pages, out, arrays["big_tile_info"], n_big, cache.block_table,
-                             n_q_heads, n_kv_heads, cache.page_size, scale)
+                             n_q_heads, n_kv_heads, cache.page_size, scale, slopes_log2=slopes_log2)
         if n_rest:
             prefill(q, cache.pages, out, arrays["rest_tile_info"], n_rest, cache.block_table, n_q_heads,
-                    n_kv_heads, head_dim, cache.page_size, window, scale)
+                    n_kv_heads, head_dim, cache.page_size, window, scale, slopes_log2)
     elif n_tiles:
         prefill(q, cache.pages, out, arrays["tile_info"], n_tiles, cache.block_table, n_q_heads, n_kv_heads,
                 head_dim, cache.page_size, window, scale, slopes_log2)

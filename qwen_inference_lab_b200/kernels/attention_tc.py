@@ -35,19 +35,25 @@ def supports(head_dim, page_size, window) -> bool:
 
 
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, page_size, scale, trace=None,
-            lib=None):
+            lib=None, slopes_log2=None):
     """q, out bfloat16 [N, Hq*128]; pages [num_pages, 2, Hkv, page_size, 128];
-    tile_info int32 [n_tiles * 4] = (first token, its position, 128, block-table row)."""
+    tile_info int32 [n_tiles * 4] = (first token, its position, 128, block-table row).
+    ``slopes_log2`` float32 [Hq] on the device: slope_h * log2(e) of a bias slope_h * (query position - key
+    position) taken off the scaled score."""
+    if slopes_log2 is not None:
+        _need(slopes_log2, "slopes_log2", torch.float32, 1)
+        if slopes_log2.shape[0] != n_q_heads:
+            raise KernelError("attention_tc: one slope per query head")
     _need(q, "q", torch.bfloat16, 2); _need(out, "out", torch.bfloat16, 2); _need(pages, "pages", torch.bfloat16, 5)
     if tuple(pages.shape[1:]) != (2, n_kv_heads, page_size, HEAD_DIM) or q.shape[1] != n_q_heads * HEAD_DIM:
         raise KernelError("attention_tc: shapes do not match the head counts")
     lib = lib or library()
     word = _fault.tensor(q.device)
     _fault.mark()
-    _check(lib, lib.qil_attn_tc_prefill(
+    _check(lib, lib.qil_attn_tc_prefill_biased(
         _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), c_int(q.shape[0]), _p(block_table),
         c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]),
-        c_float(scale), _p(word), _p(trace), _stream()), "attention (128-token tiles)")
+        c_float(scale), _p(slopes_log2), _p(word), _p(trace), _stream()), "attention (128-token tiles)")
 
 
 def check(wait=True) -> None:

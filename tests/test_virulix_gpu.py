@@ -191,6 +191,24 @@ def test_a_far_key_through_the_mixer_in_prompts_and_in_decoding(dtype, far, quer
     assert out[:, 64:].abs().max() == 0
 
 
+def test_heads_of_128_take_the_tensor_memory_kernel_with_the_distance_bias(monkeypatch):
+    """Whole 128-token tiles of a prompt go to the tcgen05 kernel, which takes the slopes too; the leftovers and single
+    tokens to the tiled ones.  The far key of the test above would be too blunt here: random rows, every position."""
+    from qwen_inference_lab_b200.kernels import attention_tc
+    calls = []
+    original = attention_tc.prefill
+    monkeypatch.setattr(attention_tc, "prefill", lambda *a, **k: (calls.append(k.get("slopes_log2") is not None), original(*a, **k))[1])
+    part, w, mixer = attention_part(torch.bfloat16, heads=4, kv_heads=2, dim=128, vdim=128, temperature=(0.3, 64))
+    x = {"a": rows(330, 64, 12), "b": rows(140, 64, 13)}
+    expected = {rid: plain.attention_mixer(v, w, "m.", mixer, low=torch.bfloat16)[0] for rid, v in x.items()}
+    body = lambda ctx, h, view: part.forward(ctx, h, view)
+    for cuts in ({"a": [330], "b": [140]}, {"a": [129, 1, 200], "b": [7, 133]}):
+        out = harness.run_part(part, 64, torch.bfloat16, body, x, cuts, page_size=16, num_pages=40)
+        for rid in x:
+            close(out[rid], expected[rid], torch.bfloat16)
+    assert calls and all(calls)
+
+
 def gla_part(dtype, heads, d, e, rank, tau, hidden=48, seed=2):
     from qwen_inference_lab_b200.parts import GatedLinearAttention
     from qwen_inference_lab_b200.models.virulix import BARE
@@ -494,3 +512,27 @@ def test_trace_run_replays_a_mixed_schedule(folders, truth, tmp_path, dtype):
     expected, low = truth["B"]
     torch_dtype = torch.float32 if dtype == "float32" else torch.bfloat16
     harness.assert_rows_close(got, expected, torch_dtype, f"virulix trace_run {dtype}", low if dtype == "bfloat16" else None)
+
+
+def test_command_line_generates_with_written_and_with_random_weights(folders, tmp_path):
+    """``python -m qwen_inference_lab_b200`` on a Virulix folder: greedy tokens as the plain implementation's; and
+    ``--random-weights`` on a folder that holds only config.json (the sizes that only tensors give take their defaults)."""
+    folder, weights, _ = folders["A"]
+    prompt = cases.random_tokens(cases.CASE_B, 9, 77)          # ids that both vocabularies hold
+    run = lambda model, *extra: subprocess.run(
+        [sys.executable, "-m", "qwen_inference_lab_b200", "--model", str(model), "--token-ids", json.dumps(prompt),
+         "--dtype", "float32", "--max-new-tokens", "4", "--pages", "16", "--page-size", "4", "--chunk-size", "5",
+         "--ignore-eos", *extra], capture_output=True, text=True, cwd=str(ROOT))
+    done = run(folder)
+    assert done.returncode == 0, done.stderr
+    tokens = json.loads(done.stdout)["token_ids"]
+    sequence = list(prompt)
+    for token in tokens:
+        assert token == int(plain.forward(sequence, weights, cases.CASE_A)[-1].argmax())
+        sequence.append(token)
+    bare = tmp_path / "bare"
+    bare.mkdir()
+    (bare / "config.json").write_text(json.dumps(cases.CASE_B))
+    done = run(bare, "--random-weights", "3")
+    assert done.returncode == 0, done.stderr
+    assert len(json.loads(done.stdout)["token_ids"]) == 4 and (bare / "model.safetensors").is_file()
