@@ -219,7 +219,7 @@ def gla_part(dtype, heads, d, e, rank, tau, hidden=48, seed=2):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("shape", [dict(heads=2, d=32, e=64, rank=16, tau=16.0), dict(heads=3, d=24, e=40, rank=4, tau=1.0),
+@pytest.mark.parametrize("shape", [dict(heads=2, d=32, e=48, rank=12, tau=9.0), dict(heads=3, d=24, e=40, rank=4, tau=1.0),
                                    dict(heads=1, d=72, e=16, rank=7, tau=5.0), dict(heads=1, d=8, e=320, rank=2, tau=3.0),
                                    dict(heads=2, d=130, e=72, rank=9, tau=8.0)])
 def test_gla_mixer_whole_cut_and_side_by_side(dtype, shape):
@@ -239,7 +239,7 @@ def test_gla_mixer_whole_cut_and_side_by_side(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("shape", [dict(heads=2, d=32, e=64, rank=16, tau=16.0), dict(heads=1, d=40, e=300, rank=3, tau=4.0)])
+@pytest.mark.parametrize("shape", [dict(heads=2, d=32, e=48, rank=12, tau=9.0), dict(heads=1, d=40, e=300, rank=3, tau=4.0)])
 def test_gla_long_portions_run_as_chunks_side_by_side(dtype, shape):
     """Portions of more than 128 tokens are cut into chunks of 64 whose states are carried over: 129 tokens (a last
     chunk of one token), 300 after a cached prefix, a long portion beside a short one and a single token; against
@@ -305,7 +305,7 @@ def experts_part(dtype, experts, top, shared, hidden=40, ff=24, seed=3):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("experts,top,shared", [(5, 2, True), (3, 1, False), (12, 3, True), (4, 4, False), (70, 5, False)])
+@pytest.mark.parametrize("experts,top,shared", [(5, 2, True), (3, 1, False), (11, 3, True), (4, 4, False), (70, 5, False)])
 def test_routed_experts_alone_and_in_a_batch(dtype, experts, top, shared):
     from qwen_inference_lab_b200.kernels import ops
     part, w, mlp = experts_part(dtype, experts, top, shared)
@@ -314,7 +314,7 @@ def test_routed_experts_alone_and_in_a_batch(dtype, experts, top, shared):
     want_chosen, want_weights = plain.route(x, w, "f.", top)
     assert torch.equal(chosen.cpu().long(), want_chosen), "the router's choice (no close calls among these logits)"
     torch.testing.assert_close(weights.cpu(), want_weights, atol=1e-5, rtol=1e-5)
-    assert len(set(want_chosen.flatten().tolist())) >= min(experts, 12), "most experts should be in use"
+    assert len(set(want_chosen.flatten().tolist())) >= min(experts, 11), "most experts should be in use"
     expected = plain.routed_feed_forward(x, w, "f.", mlp, low=low_of(dtype))
     body = lambda ctx, h, view: part.forward(ctx, h)
     together = harness.run_part(part, 40, dtype, body, {"a": x[:99], "b": x[99:]}, {"a": [99], "b": [51]})
