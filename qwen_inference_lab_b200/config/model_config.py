@@ -121,7 +121,7 @@ def read_config_json(directory) -> dict:
 
 
 _MIXER_KEYS = {
-    "attention": {"heads", "kv_heads", "dim", "vdim", "scale"},
+    "attention": {"heads", "kv_heads", "dim", "vdim"},         # "scale" defaults to dim^-1/2
     "gla": {"heads", "dim", "vdim", "tau"},
 }
 

@@ -25,6 +25,7 @@
 #define MOE_BK 16
 #define MOE_MAX_EXPERTS 1024
 #define MOE_MAX_TOP 64
+#define MOE_ONE_BLOCK_PAIRS 512   // up to here one block groups the pairs, in ascending order inside every expert
 
 // ------------------------------------------------------------------ route
 __device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
@@ -473,13 +474,14 @@ extern "C" int qil_moe_route(const void* x, const void* router, const void* bias
 }
 
 extern "C" int qil_moe_tile_rows() { return MOE_BM; }
+extern "C" int qil_moe_one_block_pairs() { return MOE_ONE_BLOCK_PAIRS; }
 
 // work: int32 [1 + n_experts] (tile count, then a cursor per expert); tiles: int32 [max_tiles, 3].
 extern "C" int qil_moe_group(const int* chosen, int n_pairs, int n_experts, int* sorted_pairs, int* work, int* tiles,
                              int max_tiles, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (n_experts <= 0 || n_experts > MOE_MAX_EXPERTS) QIL_REFUSE("moe_group: %d experts", n_experts);
-    if (n_pairs <= 4096) {
+    if (n_pairs <= MOE_ONE_BLOCK_PAIRS) {
         qil_launch_chained(moe_group_kernel, dim3(1), dim3(1024), 0, stream, chosen, n_pairs, n_experts, sorted_pairs,
                            work, tiles, max_tiles);
     } else {

@@ -623,7 +623,7 @@ def moe_experts(x, chosen, weights, gate_w, up_w, down_w, kind, *, limit=0.0, al
     y = torch.empty((pairs, width), dtype=torch.float32, device=x.device)
     act, wt = c_int(dtype_code(x.dtype)), c_int(dtype_code(gate_w.dtype))
     _check(lib, lib.qil_moe_group(_p(chosen), c_int(pairs), c_int(experts), _p(sorted_pairs), _p(info), _p(tiles),
-                                  c_int(max_tiles), _stream()), "moe_group", kernels=1 if pairs <= 4096 else 2)
+                                  c_int(max_tiles), _stream()), "moe_group", kernels=1 if pairs <= lib.qil_moe_one_block_pairs() else 2)
     _check(lib, lib.qil_moe_gate_up(_p(x), c_int(width), _p(gate_w), _p(up_w), _p(tiles), _p(info), c_int(max_tiles),
                                     _p(sorted_pairs), c_int(top), _p(hidden), c_int(ff), c_int(width),
                                     c_int(ACTIVATIONS[kind]), c_float(limit), c_float(alpha), act, wt, _stream()),

@@ -54,7 +54,7 @@ def _mixer(width, kind, m, prefix, eps, shapes):
     if kind == "attention":
         temperature = m.get("q_temp")
         return GroupedQueryAttention(
-            width, m["heads"], m["kv_heads"], m["dim"], names=names, bias=True, out_bias=False, scale=m["scale"],
+            width, m["heads"], m["kv_heads"], m["dim"], names=names, bias=True, out_bias=False, scale=m.get("scale"),
             v_head_dim=m["vdim"], distance_slopes=distance_slopes(m["heads"]),
             q_temperature=(temperature["coef"], temperature["every"]) if temperature else None,
             reads_shared_cache=m.get("kv_from") is not None, suffixes=BARE)

@@ -536,3 +536,17 @@ def test_command_line_generates_with_written_and_with_random_weights(folders, tm
     done = run(bare, "--random-weights", "3")
     assert done.returncode == 0, done.stderr
     assert len(json.loads(done.stdout)["token_ids"]) == 4 and (bare / "model.safetensors").is_file()
+
+
+def test_a_checkpoint_may_leave_out_the_second_norm_of_a_layer_without_feed_forward(folders, tmp_path):
+    from qwen_inference_lab_b200.weights import SafetensorsFile, write_safetensors
+    folder, weights, requests = folders["A"]
+    with SafetensorsFile(folder / "model.safetensors") as f:
+        tensors = {name: f.tensor(name).clone() for name in f.keys() if name != "l2.norm2"}
+    (tmp_path / "config.json").write_text((folder / "config.json").read_text())
+    write_safetensors(tmp_path / "model.safetensors", tensors)
+    rows_of = {}
+    for source in (folder, tmp_path):
+        _, cache, runner = harness.build_engine_parts(source, torch.float32, num_pages=40, page_size=4)
+        rows_of[source] = harness.run_schedule(runner, cache, harness.whole_schedule({"r1": requests["r1"], "r2": requests["r2"]}))
+    assert all(torch.equal(rows_of[folder][key], rows_of[tmp_path][key]) for key in rows_of[folder])
