@@ -40,7 +40,7 @@ __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
 }
 
 template <typename T, typename W>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W* __restrict__ bias, int width,
                  int n_experts, int top, int* __restrict__ chosen, float* __restrict__ weights) {
     __shared__ float logits[MOE_MAX_EXPERTS];
@@ -54,23 +54,38 @@ moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W*
     // A lane takes runs of 8 values, 16 or 32 bytes a load, four runs in flight per operand; its partial sum runs in
     // ascending order, the lanes' sums meet in a fixed tree: the same bits whatever else is in the batch.
     const bool wide = width % 8 == 0 && (((uintptr_t)x | (uintptr_t)router) & 15) == 0;
-    for (int e = warp; e < n_experts; e += 4) {
-        const W* w = router + (size_t)e * width;
-        float dot = 0.f;
-        if (wide) {
-#pragma unroll 4
+    const int warps = blockDim.x >> 5;
+    if (wide) {
+        // four experts at a time share every load of the token's row and keep four weight loads in flight
+        for (int e0 = warp * 4; e0 < n_experts; e0 += warps * 4) {
+            float dot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
             for (int i = lane * 8; i < width; i += 256) {
-                float a[8], b[8];
+                float a[8];
                 load8(row + i, a);
-                load8(w + i, b);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) dot = fmaf(a[j], b[j], dot);
+                for (int u = 0; u < 4; ++u) {
+                    if (e0 + u >= n_experts) continue;
+                    float b[8];
+                    load8(router + (size_t)(e0 + u) * width + i, b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dot[u] = fmaf(a[j], b[j], dot[u]);
+                }
             }
-        } else {
-            for (int i = lane; i < width; i += 32) dot = fmaf(to_f32<T>(row[i]), to_f32<W>(w[i]), dot);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float total = warp_sum(dot[u]);
+                if (lane == 0 && e0 + u < n_experts) logits[e0 + u] = total + (bias != nullptr ? to_f32<W>(bias[e0 + u]) : 0.f);
+            }
         }
-        dot = warp_sum(dot);
-        if (lane == 0) logits[e] = dot + (bias != nullptr ? to_f32<W>(bias[e]) : 0.f);
+    } else {
+        for (int e = warp; e < n_experts; e += warps) {
+            const W* w = router + (size_t)e * width;
+            float dot = 0.f;
+            for (int i = lane; i < width; i += 32) dot = fmaf(to_f32<T>(row[i]), to_f32<W>(w[i]), dot);
+            dot = warp_sum(dot);
+            if (lane == 0) logits[e] = dot + (bias != nullptr ? to_f32<W>(bias[e]) : 0.f);
+        }
     }
     __syncthreads();
     if (warp != 0) return;
@@ -468,7 +483,7 @@ extern "C" int qil_moe_route(const void* x, const void* router, const void* bias
     if (n_experts <= 0 || n_experts > MOE_MAX_EXPERTS || top <= 0 || top > n_experts || top > MOE_MAX_TOP || width <= 0)
         QIL_REFUSE("moe_route: %d experts (at most %d), %d of them per token, width %d", n_experts, MOE_MAX_EXPERTS, top, width);
     QIL_DISPATCH_2(act_dtype, weight_dtype,
-        qil_launch_chained(moe_route_kernel<T, W>, dim3(n_tokens), dim3(128), 0, stream, (const T*)x, (const W*)router,
+        qil_launch_chained(moe_route_kernel<T, W>, dim3(n_tokens), dim3(256), 0, stream, (const T*)x, (const W*)router,
                            (const W*)bias, width, n_experts, top, chosen, weights));
     QIL_CHECK_LAUNCH();
 }
