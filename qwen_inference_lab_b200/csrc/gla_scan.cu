@@ -204,10 +204,22 @@ gla_carry_kernel(float* __restrict__ chunk_state, const float* __restrict__ deca
     const int row = carry[3 * blockIdx.y], first = carry[3 * blockIdx.y + 1], chunks = carry[3 * blockIdx.y + 2];
     const size_t channel = i / e;                 // head * d + key channel
     float s = slots[(size_t)row * per_state + i];
-    for (int c = first; c < first + chunks; ++c) {
-        const float own = chunk_state[(size_t)c * per_state + i];
-        chunk_state[(size_t)c * per_state + i] = s;
-        s = fmaf(decay_product[(size_t)c * n_heads * d + channel], s, own);
+    // four chunks at a time: their loads are all under way before the first is used (a thread reads and writes
+    // only its own element of every chunk, so the order of loads and stores between chunks is free)
+    for (int c0 = first; c0 < first + chunks; c0 += 4) {
+        float own[4], decay[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const bool real = c0 + u < first + chunks;
+            own[u] = real ? chunk_state[(size_t)(c0 + u) * per_state + i] : 0.f;
+            decay[u] = real ? decay_product[(size_t)(c0 + u) * n_heads * d + channel] : 1.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (c0 + u >= first + chunks) break;
+            chunk_state[(size_t)(c0 + u) * per_state + i] = s;
+            s = fmaf(decay[u], s, own[u]);
+        }
     }
     slots[(size_t)row * per_state + i] = s;
 }
