@@ -5,8 +5,10 @@ Every call of the model's order may own a cache: paged keys and values
 the same spec form a *group*.  A key/value group has its own page pool, its own
 free list and one block table per request; a page id addresses the same slot range
 in every member layer's plane, as in the reference's pool (qil/cache.py:47-49).
-A group with a window gives pages back as soon as the window has passed them; the
-others keep theirs until the request ends.  A state group is an array with one
+A group with a window gives pages back as soon as the window has passed them, a group
+whose layers read only the current chunk of positions as soon as a chunk is over; the
+others keep theirs until the request ends.  A call may own several caches (pages and a
+state slot beside them): its spec is then a tuple of specs and its view a tuple of views.  A state group is an array with one
 slot per request row, zeroed at admission.  Whoever runs requests may keep state of
 its own in such slots too (``request_state``: the engine keeps each request's sampling
 settings and draw count there), beside the slots that layers own.
@@ -78,7 +80,18 @@ class _KVGroup:
         pages = self.pages_for(limit)
         if self.spec.window > 0:
             pages = min(pages, self.pages_for(self.spec.window + max_step_tokens) + 1)
+        if self.spec.chunk > 0:
+            pages = min(pages, self.pages_for(self.spec.chunk + max_step_tokens) + 1)
         return pages
+
+    def first_needed(self, end):
+        """The first logical page that a request whose next position is ``end`` may still read."""
+        first = 0
+        if self.spec.window > 0:
+            first = max(first, max(0, end - self.spec.window + 1) // self.page_size)
+        if self.spec.chunk > 0:
+            first = max(first, (end // self.spec.chunk * self.spec.chunk) // self.page_size)
+        return first
 
     @property
     def unreserved(self):
@@ -98,26 +111,29 @@ class CacheManager:
         self.max_step_tokens = int(max_step_tokens or max_context)
         self.device, self.dtype = torch.device(device), dtype
         self.specs = list(specs)
-        windowed = any(isinstance(s, KVCacheSpec) and s.window > 0 for s in self.specs)
+        flat = [one for spec in self.specs for one in (spec if isinstance(spec, tuple) else (spec,))]
+        windowed = any(isinstance(s, KVCacheSpec) and (s.window > 0 or s.chunk > 0) for s in flat)
         span = max_context if windowed else min(max_context, num_pages * page_size)
         self.table_width = (span + page_size - 1) // page_size
         self.kv_groups: list = []
         self.state_groups: list = []   # (spec, members, tensor)
-        self._owner: dict = {}         # call index -> ("kv", group, member) | ("state", group, member)
+        self._owner: dict = {}         # (call index, part of its spec) -> ("kv", group, member) | ("state", group, member)
         by_spec: dict = {}
         for call, spec in enumerate(self.specs):
-            if spec is not None:
-                by_spec.setdefault(spec, []).append(call)
-        for spec, members in by_spec.items():
+            for part, one in enumerate(spec if isinstance(spec, tuple) else (spec,)):
+                if one is not None:
+                    by_spec.setdefault(one, []).append((call, part))
+        for spec, owners in by_spec.items():
+            members = [call for call, _ in owners]
             if isinstance(spec, KVCacheSpec):
                 group = _KVGroup(spec, members, num_pages, page_size, max_requests, self.table_width, dtype, device)
-                for m, call in enumerate(members):
-                    self._owner[call] = ("kv", len(self.kv_groups), m)
+                for m, owner in enumerate(owners):
+                    self._owner[owner] = ("kv", len(self.kv_groups), m)
                 self.kv_groups.append(group)
             elif isinstance(spec, StateSpec):
                 tensor = torch.zeros((len(members), max_requests, *spec.shape), dtype=spec.dtype, device=device)
-                for m, call in enumerate(members):
-                    self._owner[call] = ("state", len(self.state_groups), m)
+                for m, owner in enumerate(owners):
+                    self._owner[owner] = ("state", len(self.state_groups), m)
                 self.state_groups.append((spec, members, tensor))
             else:
                 raise CacheError(f"unknown cache spec {spec!r}")
@@ -220,15 +236,16 @@ class CacheManager:
             g.dirty.add(row)
 
     def advance(self, request_id, end) -> None:
-        """Record that positions below ``end`` are written; give back pages a window has passed."""
+        """Record that positions below ``end`` are written; give back pages that a window has passed or whose
+        chunk is over."""
         if end < self.progress[request_id]:
             raise CacheError("cache progress cannot move backwards")
         self.progress[request_id] = end
         row = self.rows[request_id]
         for g in self.kv_groups:
-            if g.spec.window <= 0:
+            if g.spec.window <= 0 and g.spec.chunk <= 0:
                 continue
-            first_needed = max(0, end - g.spec.window + 1) // g.page_size
+            first_needed = g.first_needed(end)
             table = g.tables[request_id]
             for index in range(g.first_live[request_id], min(first_needed, len(table))):
                 if table[index] >= 0:
@@ -286,19 +303,24 @@ class CacheManager:
 
     def views(self, order=None) -> list:
         """One view per call of the order (``order[i].reads_cache_of`` redirects to the owner)."""
+        def view(owner):
+            if owner is None:
+                return None
+            if owner[0] == "kv":
+                g = self.kv_groups[owner[1]]
+                return KVCacheView(g.storage[owner[2]], g.dev_table, g.page_size, g.spec.window)
+            return StateView(self.state_groups[owner[1]][2][owner[2]])
+
         result = []
         for call in range(len(self.specs)):
             source = call
             if order is not None and order[call].reads_cache_of is not None:
                 source = order[call].reads_cache_of
-            owner = self._owner.get(source)
-            if owner is None:
-                result.append(None)
-            elif owner[0] == "kv":
-                g = self.kv_groups[owner[1]]
-                result.append(KVCacheView(g.storage[owner[2]], g.dev_table, g.page_size, g.spec.window))
+            spec = self.specs[source]
+            if isinstance(spec, tuple):
+                result.append(tuple(view(self._owner.get((source, part))) for part in range(len(spec))))
             else:
-                result.append(StateView(self.state_groups[owner[1]][2][owner[2]]))
+                result.append(view(self._owner.get((source, 0))))
         return result
 
     def poison(self, value=float("nan")) -> None:

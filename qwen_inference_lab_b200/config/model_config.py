@@ -200,3 +200,106 @@ class VirulixConfig:
 
     def __eq__(self, other):
         return isinstance(other, VirulixConfig) and self.to_dict() == other.to_dict()
+
+
+def _positive_int(value) -> bool:
+    return type(value) is int and value >= 1
+
+
+class DebisunConfig:
+    """Debisun: a decoder whose layers are listed one by one in config.json.
+
+    ``vocab``, ``width``, ``norm.eps``, ``token_side.dim`` (the size of a layer's slice of the per-token side
+    table; absent: no side input) and ``layers``: every layer is an ``attention`` mixer with its sizes and
+    constants (``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``conv`` taps, ``softcap``, ``bias_max``,
+    ``mask.size``) and a feed-forward (``mlp``: ``dense`` with ``ff``; ``moe`` with ``router`` (``experts``,
+    ``top``, ``identity``, ``scale``), ``expert.ff`` and optionally ``shared.ff``; or null).  The configuration is
+    kept as the dictionary it came in; this class checks it and answers the few questions the engine asks.
+    The number of rows of a layer's distance table is a size that only the tensor gives.  The design has no
+    position table: ``max_positions`` (not a key of the design; 2**20 unless given) only bounds a request.
+    """
+    architecture = "Debisun"
+    model_type = "debisun"
+
+    def __init__(self, data: dict):
+        self.data = data
+        for key in ("vocab", "width"):
+            if not _positive_int(data.get(key)):
+                raise ConfigError(f"{key} must be a positive integer, got {data.get(key)!r}")
+        eps = (data.get("norm") or {}).get("eps")
+        if isinstance(eps, bool) or not isinstance(eps, (int, float)) or not eps > 0:
+            raise ConfigError(f"norm.eps must be a positive number, got {eps!r}")
+        side = data.get("token_side")
+        if side is not None and not _positive_int((side or {}).get("dim")):
+            raise ConfigError(f"token_side.dim must be a positive integer, got {side!r}")
+        layers = data.get("layers")
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("layers must be a non-empty list")
+        for index, layer in enumerate(layers):
+            where = f"layers[{index}]"
+            if layer.get("type") != "attention":
+                raise ConfigError(f"{where}.type {layer.get('type')!r} is not 'attention'")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"{where}.mixer must be an object")
+            for key in ("heads", "kv_heads", "dim", "vdim"):
+                if not _positive_int(mixer.get(key)):
+                    raise ConfigError(f"{where}.mixer.{key} must be a positive integer, got {mixer.get(key)!r}")
+            if mixer["heads"] % mixer["kv_heads"]:
+                raise ConfigError(f"{where}: {mixer['heads']} heads do not divide into {mixer['kv_heads']} kv heads")
+            for key in ("scale", "softcap"):
+                value = mixer.get(key)
+                if key == "softcap" and value is None:
+                    continue
+                if isinstance(value, bool) or not isinstance(value, (int, float)) or not value > 0:
+                    raise ConfigError(f"{where}.mixer.{key} must be a positive number, got {value!r}")
+            taps = mixer.get("conv")
+            if taps is not None and not _positive_int(taps):
+                raise ConfigError(f"{where}.mixer.conv must be a positive number of taps, got {taps!r}")
+            if not _positive_int(mixer.get("bias_max")):
+                raise ConfigError(f"{where}.mixer.bias_max must be a positive integer, got {mixer.get('bias_max')!r}")
+            mask = mixer.get("mask")
+            if mask is not None and not _positive_int((mask or {}).get("size")):
+                raise ConfigError(f"{where}.mixer.mask.size must be a positive integer, got {mask!r}")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if mlp.get("kind") == "dense":
+                if not _positive_int(mlp.get("ff")):
+                    raise ConfigError(f"{where}.mlp.ff must be a positive integer")
+            elif mlp.get("kind") == "moe":
+                router, expert = mlp.get("router") or {}, mlp.get("expert") or {}
+                if not _positive_int(router.get("experts")) or not _positive_int(router.get("top")) \
+                        or not _positive_int(expert.get("ff")):
+                    raise ConfigError(f"{where}.mlp needs router.experts, router.top and expert.ff")
+                identity = router.get("identity", 0)
+                if type(identity) is not int or identity < 0:
+                    raise ConfigError(f"{where}.mlp.router.identity must be a non-negative integer")
+                if router["top"] > router["experts"] + identity:
+                    raise ConfigError(f"{where}.mlp: {router['top']} of {router['experts']} + {identity} router outputs")
+                scale = router.get("scale", 1.0)
+                if isinstance(scale, bool) or not isinstance(scale, (int, float)):
+                    raise ConfigError(f"{where}.mlp.router.scale must be a number")
+                shared = mlp.get("shared")
+                if shared is not None and not _positive_int(shared.get("ff")):
+                    raise ConfigError(f"{where}.mlp.shared.ff must be a positive integer")
+            else:
+                raise ConfigError(f"{where}.mlp.kind {mlp.get('kind')!r} is neither dense nor moe")
+        self.vocab_size, self.width, self.eps = data["vocab"], data["width"], float(eps)
+        self.side_dim = side["dim"] if side else 0
+        self.layers = layers
+        self.max_positions = int(data.get("max_positions", 1 << 20))
+        eos = data.get("eos_token_id")
+        self.eos_token_ids = frozenset() if eos is None else frozenset(eos if isinstance(eos, list) else [eos])
+
+    @classmethod
+    def from_dict(cls, data: dict) -> "DebisunConfig":
+        if data.get("architecture", cls.architecture) != cls.architecture:
+            raise ConfigError(f"architecture {data.get('architecture')!r} is not {cls.architecture}")
+        return cls(json.loads(json.dumps(data)))
+
+    def to_dict(self) -> dict:
+        return json.loads(json.dumps(self.data)) | {"architecture": self.architecture}
+
+    def __eq__(self, other):
+        return isinstance(other, DebisunConfig) and self.to_dict() == other.to_dict()

@@ -20,7 +20,23 @@
 // that grows with distance may be taken off the scaled score (`slopes`, one per
 // query head): score = q.k * scale - slope_h * (i - j) for the query at position i
 // and the key at position j.
+//
+// Further options of the score, all in float32 (`ScoreOptions`):
+//   softcap     score <- cap * tanh(score / cap), applied to the scaled product before any bias
+//   dist_bias   a learned bias per (query head, distance i - j): float32 [Hq][dist_len], distances beyond the
+//               table read its last entry (the caller expands buckets of distances into this table)
+//   chunk       position i sees only the j <= i with floor(i / chunk) = floor(j / chunk), chunks counted
+//               from position 0 of the sequence
+//   sink        one is added to the softmax's denominator: a key of score 0 that has no value
 #include "common.cuh"
+
+struct ScoreOptions {
+    float softcap;            // 0: none
+    const float* dist_bias;   // null: none
+    int dist_len;
+    int chunk;                // 0: none
+    int sink;                 // 0 or 1
+};
 
 #define GEN_TILE 128
 #define GEN_MAX_D 512
@@ -32,7 +48,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
                          const int* __restrict__ positions, const int* __restrict__ token_row,
                          const int* __restrict__ block_table, int table_stride,
                          int n_q_heads, int n_kv_heads, int head_dim, int v_dim, int page_size, int num_pages,
-                         int window, float scale, const float* __restrict__ slopes) {
+                         int window, float scale, const float* __restrict__ slopes, ScoreOptions opt) {
     extern __shared__ long long smem_ll[];
     long long* row_off = smem_ll;                      // [GEN_TILE] element offset of each key row, -1 if none
     long long* val_off = row_off + GEN_TILE;           // [GEN_TILE] element offset of each value row
@@ -45,14 +61,17 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
     const int token = blockIdx.x, head = blockIdx.y;
     const int kv_head = head / (n_q_heads / n_kv_heads);
     const int pos = positions[token];
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (opt.chunk > 0 && pos >= 0) lo = max(lo, pos / opt.chunk * opt.chunk);
     const int* table = block_table + (size_t)token_row[token] * table_stride;
+    const float* bias_row = opt.dist_bias != nullptr ? opt.dist_bias + (size_t)head * opt.dist_len : nullptr;
 
     const float slope = slopes != nullptr ? slopes[head] : 0.f;
     const T* qrow = q + ((size_t)token * n_q_heads + head) * head_dim;
     for (int d = tid; d < head_dim; d += GEN_TILE) qs[d] = to_f32<T>(qrow[d]);
 
-    float m_run = -INFINITY, l_run = 0.f;
+    // the sink is a key of score 0 and weight exp(0 - max) that adds nothing to the sum of values
+    float m_run = opt.sink ? 0.f : -INFINITY, l_run = opt.sink ? 1.f : 0.f;
     float acc[GEN_DPT];
 #pragma unroll
     for (int i = 0; i < GEN_DPT; ++i) acc[i] = 0.f;
@@ -88,7 +107,13 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv_cache
             for (int dd = 0; dd < chunk; ++dd) dot = fmaf(qs[d0 + dd], ks[tid * 33 + dd], dot);
             __syncthreads();
         }
-        const float score = (valid && off >= 0) ? dot * scale - slope * (float)(pos - key) : -INFINITY;
+        float score = -INFINITY;
+        if (valid && off >= 0) {
+            score = dot * scale;
+            if (opt.softcap > 0.f) score = opt.softcap * tanhf(score / opt.softcap);
+            score -= slope * (float)(pos - key);
+            if (bias_row != nullptr) score += bias_row[min(pos - key, opt.dist_len - 1)];
+        }
         const float tile_max = block_max(score, red);
         const float m_new = fmaxf(m_run, tile_max);
         const float p = (score == -INFINITY) ? 0.f : expf(score - m_new);
@@ -122,7 +147,7 @@ extern "C" int qil_attention_generic(
     const void* q, const void* kv_cache, void* out, const int* positions, const int* token_row,
     const int* block_table, int table_stride, int n_tokens, int n_q_heads, int n_kv_heads,
     int head_dim, int v_dim, int page_size, int num_pages, int window, float scale, const float* slopes,
-    int act_dtype, cudaStream_t stream) {
+    float softcap, const float* dist_bias, int dist_len, int chunk, int sink, int act_dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > GEN_MAX_D || v_dim <= 0 || v_dim > GEN_MAX_D)
         QIL_REFUSE("attention_generic: head sizes %d and %d must lie in 1..%d", head_dim, v_dim, GEN_MAX_D);
@@ -130,12 +155,15 @@ extern "C" int qil_attention_generic(
         QIL_REFUSE("attention_generic: %d query heads do not divide into %d kv heads", n_q_heads, n_kv_heads);
     if (n_q_heads > 65535) QIL_REFUSE("attention_generic: too many heads (%d)", n_q_heads);
     if (page_size <= 0 || window < 0) QIL_REFUSE("attention_generic: page_size %d window %d", page_size, window);
+    if (softcap < 0.f || chunk < 0 || (dist_bias != nullptr && dist_len < 1))
+        QIL_REFUSE("attention_generic: softcap %g chunk %d distance table of %d", softcap, chunk, dist_len);
+    ScoreOptions opt = {softcap, dist_bias, dist_len, chunk, sink ? 1 : 0};
     dim3 grid(n_tokens, n_q_heads);
     const size_t smem = (size_t)(head_dim + GEN_TILE * 33 + GEN_TILE + 32) * sizeof(float)
                         + 2 * GEN_TILE * sizeof(long long);
     QIL_DISPATCH_1(act_dtype,
         (attention_generic_kernel<T><<<grid, GEN_TILE, smem, stream>>>(
             (const T*)q, (const T*)kv_cache, (T*)out, positions, token_row, block_table, table_stride,
-            n_q_heads, n_kv_heads, head_dim, v_dim, page_size, num_pages, window, scale, slopes)));
+            n_q_heads, n_kv_heads, head_dim, v_dim, page_size, num_pages, window, scale, slopes, opt)));
     QIL_CHECK_LAUNCH();
 }

@@ -238,6 +238,34 @@ extern "C" int qil_add_inplace(void* x, const void* y, long long total, int act_
     QIL_CHECK_LAUNCH();
 }
 
+
+// ---------------------------------------------------------------- scaled add
+// x[r][c] += scale[c] * y[r][c]: a branch joins the residual stream through a learned scale per feature.
+// float32 arithmetic; x and y may differ in type (a float32 stream, bfloat16 branch).
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256)
+scaled_add_kernel(TX* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ scale, size_t total, int width) {
+    qil_wait_for_producer();
+    qil_release_consumer();
+    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256)
+        x[i] = from_f32<TX>(fmaf(scale[i % width], to_f32<TY>(y[i]), to_f32<TX>(x[i])));
+}
+
+extern "C" int qil_scaled_add(void* x, int x_dtype, const void* y, int y_dtype, const float* scale, int n_rows,
+                              int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0) QIL_REFUSE("scaled_add: width %d", width);
+    const size_t total = (size_t)n_rows * width;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+#define QIL_GO(TX, TY) qil_launch_chained(scaled_add_kernel<TX, TY>, dim3(blocks), dim3(256), 0, stream, (TX*)x, (const TY*)y, scale, total, width)
+    if (x_dtype == QIL_F32 && y_dtype == QIL_F32) QIL_GO(float, float);
+    else if (x_dtype == QIL_F32 && y_dtype == QIL_BF16) QIL_GO(float, bf16);
+    else if (x_dtype == QIL_BF16 && y_dtype == QIL_BF16) QIL_GO(bf16, bf16);
+    else if (x_dtype == QIL_BF16 && y_dtype == QIL_F32) QIL_GO(bf16, float);
+    else QIL_REFUSE("scaled_add: dtypes %d += %d", x_dtype, y_dtype);
+#undef QIL_GO
+    QIL_CHECK_LAUNCH();
+}
 // ---------------------------------------------------------------- token ids that are still on the device
 // token_ids[pairs[2i]] = source[pairs[2i + 1]]: a step may be queued before the host has read the tokens
 // that the step before it sampled; their places in the step's token list are filled in here, on the

@@ -1,4 +1,4 @@
-// C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ residual[M,N]) with float32 FMA on the
+// C[M,N] = (A[M,K] * W[N,K]^T (+ bias[N])) (* col_scale[N]) (+ residual[M,N]) with float32 FMA on the
 // CUDA cores: the matrix product of the true 32-bit path (no TF32, no tensor
 // cores), also used when a weight is stored in float32 inside a bfloat16 model.
 //
@@ -16,7 +16,8 @@
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const TA* __restrict__ A, const TW* __restrict__ Wt, const TW* __restrict__ bias,
-                const TA* residual, TA* C, int M, int N, int K, int lda) {
+                const TA* residual, TA* C, int M, int N, int K, int lda,
+                const float* __restrict__ col_scale) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -68,6 +69,7 @@ gemm_f32_kernel(const TA* __restrict__ A, const TW* __restrict__ Wt, const TW* _
             if (n >= N) continue;
             float v = acc[i][j];
             if (bias != nullptr) v += to_f32<TW>(bias[n]);
+            if (col_scale != nullptr) v *= col_scale[n];
             if (residual != nullptr) v = to_f32<TA>(residual[(size_t)m * N + n]) + v;
             C[(size_t)m * N + n] = from_f32<TA>(v);
         }
@@ -77,13 +79,13 @@ gemm_f32_kernel(const TA* __restrict__ A, const TW* __restrict__ Wt, const TW* _
 // residual may alias C (each element is read and written by the same thread).
 extern "C" int qil_gemm_f32(const void* A, int lda, const void* Wt, const void* bias, const void* residual,
                             void* C, int M, int N, int K, int act_dtype, int weight_dtype,
-                            cudaStream_t stream) {
+                            const float* col_scale, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || lda < K) QIL_REFUSE("gemm_f32: K %d lda %d", K, lda);
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) QIL_REFUSE("gemm_f32: M %d is too large for one launch", M);
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         (gemm_f32_kernel<T, W><<<grid, 256, 0, stream>>>((const T*)A, (const W*)Wt, (const W*)bias,
-                                                        (const T*)residual, (T*)C, M, N, K, lda)));
+                                                        (const T*)residual, (T*)C, M, N, K, lda, col_scale)));
     QIL_CHECK_LAUNCH();
 }

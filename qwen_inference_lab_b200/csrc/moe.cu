@@ -17,6 +17,17 @@
 // ascending order with one accumulator: a pair's result does not depend on which rows share its tile.
 // bfloat16 rows and weights whose width is a multiple of 8 take the tensor cores (further down).
 // The activation is the clamped swish of gated_activation.cu (kind 2) or silu (kind 0).
+//
+// Other designs of routing and experts, as options of the same kernels:
+//   route, mode 1   scores = softmax over all outputs of the router; the choice goes by score + correction[e],
+//                   the weights are the chosen scores alone, divided by their sum (+ 1e-20), times weight_scale.
+//                   One more row behind the router's (`gate_logit`) is a dot product that is handed out as it is:
+//                   the logit of a gate, one number per token, for an expert that every token uses.
+//   experts         without a gate matrix: h = act(A W_up[e]^T) with act the squared relu (kind 3), silu or gelu.
+//   identity        router outputs from `n_experts` on name no expert: grouping skips them and combine adds
+//                   weight * x, the token's own row.
+//   combine         out = residual + col_scale * (sum + sigmoid(gate_logit[t]) * extra[t]): a learned scale per
+//                   feature on the whole feed-forward, `extra` the float32 output of the expert that every token uses.
 #include "common.cuh"
 
 #define MOE_BM 128         // rows of a tile of the list (the float32 kernel takes it as two halves of MOE_FM)
@@ -42,8 +53,11 @@ __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
 template <typename T, typename W>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W* __restrict__ bias, int width,
-                 int n_experts, int top, int* __restrict__ chosen, float* __restrict__ weights) {
+                 int n_outputs, int top, int* __restrict__ chosen, float* __restrict__ weights, int mode,
+                 const float* __restrict__ correction, float weight_scale, float* __restrict__ gate_logit) {
     __shared__ float logits[MOE_MAX_EXPERTS];
+    __shared__ float choice[MOE_MAX_EXPERTS];
+    const int n_experts = n_outputs + (gate_logit != nullptr ? 1 : 0);     // rows of `router` (the gate's row is the last)
     __shared__ float sel_p[MOE_MAX_TOP];
     __shared__ int sel_at[MOE_MAX_TOP];
     qil_wait_for_producer();
@@ -89,11 +103,57 @@ moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W*
     }
     __syncthreads();
     if (warp != 0) return;
+    if (gate_logit != nullptr) {
+        if (lane == 0) gate_logit[token] = logits[n_outputs];
+    }
+    if (mode == 1) {
+        // softmax over all outputs; the choice by score + correction, the weights from the scores alone
+        float peak = -INFINITY;
+        for (int e = lane; e < n_outputs; e += 32) peak = fmaxf(peak, logits[e]);
+        peak = warp_max(peak);
+        float sum = 0.f;
+        for (int e = lane; e < n_outputs; e += 32) sum += expf(logits[e] - peak);
+        sum = warp_sum(sum);
+        for (int e = lane; e < n_outputs; e += 32) {
+            const float score = expf(logits[e] - peak) / sum;
+            logits[e] = score;
+            choice[e] = score + (correction != nullptr ? correction[e] : 0.f);
+        }
+        __syncwarp();
+        float picked = 0.f;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int at = n_outputs;
+            for (int e = lane; e < n_outputs; e += 32) {
+                const float v = choice[e];
+                if (v > best) { best = v; at = e; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float other = __shfl_xor_sync(0xffffffffu, best, o);
+                const int other_at = __shfl_xor_sync(0xffffffffu, at, o);
+                if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+            }
+            if (at >= n_outputs) at = k;                               // non-finite scores: still name an output
+            const float score = logits[at];
+            picked += score;
+            if (lane == 0) {
+                sel_at[k] = at;
+                sel_p[k] = score;
+                choice[at] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        for (int k = lane; k < top; k += 32) {
+            chosen[token * top + k] = sel_at[k];
+            weights[token * top + k] = sel_p[k] / (picked + 1e-20f) * weight_scale;
+        }
+        return;
+    }
     float best_first = 0.f, total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
-        int at = n_experts;
-        for (int e = lane; e < n_experts; e += 32) {
+        int at = n_outputs;
+        for (int e = lane; e < n_outputs; e += 32) {
             const float v = logits[e];
             if (v > best) { best = v; at = e; }       // ascending e: the lower index wins a tie inside a lane
         }
@@ -102,7 +162,7 @@ moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W*
             const int other_at = __shfl_xor_sync(0xffffffffu, at, o);
             if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
         }
-        if (at >= n_experts) { at = k; best = -INFINITY; }      // non-finite logits: still name an expert
+        if (at >= n_outputs) { at = k; best = -INFINITY; }      // non-finite logits: still name an expert
         if (k == 0) best_first = best;
         const float p = best == -INFINITY ? 0.f : expf(best - best_first);
         total += p;
@@ -205,15 +265,25 @@ __device__ __forceinline__ float expert_activation(int kind, float g, float u, f
     return g / (1.f + expf(-alpha * g)) * (u + 1.f);
 }
 
-// DUAL: two weight stacks (gate, up) [experts, n_out, k]; rows of A gathered by pair / top; activation; output
-// in grouped order.  Otherwise one stack; rows of A in grouped order; output float32 at the pair's place, scaled.
-template <typename T, typename W, bool DUAL>
+// An expert without a gate matrix: 0 silu, 1 gelu (tanh), 3 squared relu.
+__device__ __forceinline__ float expert_plain_activation(int kind, float z) {
+    if (kind == 0) return z / (1.f + expf(-z));
+    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+}
+
+// MODE 1 (DUAL): two weight stacks (gate, up) [experts, n_out, k]; rows of A gathered by pair / top; activation; output
+// in grouped order.  MODE 2: the same with one stack and an activation without a gate.  MODE 0: one stack; rows of A in
+// grouped order; output float32 at the pair's place, scaled.
+template <typename T, typename W, int MODE>
 __global__ void __launch_bounds__(256)
 moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w0, const W* __restrict__ w1,
                        const int* __restrict__ tiles, const int* __restrict__ info,
                        const int* __restrict__ sorted_pairs, int top, const float* __restrict__ pair_weight,
                        T* __restrict__ hidden, float* __restrict__ y, int n_out, int K, int kind, float limit,
                        float alpha) {
+    constexpr bool DUAL = MODE == 1, UP = MODE != 0;
     __shared__ float As[MOE_BK][MOE_FM + 4];
     __shared__ float W0s[MOE_BK][MOE_BN + 4];
     __shared__ float W1s[DUAL ? MOE_BK : 1][MOE_BN + 4];
@@ -228,7 +298,7 @@ moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w
     if (rows <= 0) return;
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int n0 = blockIdx.x * MOE_BN;
-    if (tid < MOE_FM) src_row[tid] = tid < rows ? (DUAL ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
+    if (tid < MOE_FM) src_row[tid] = tid < rows ? (UP ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
     __syncthreads();
     const W* e0 = w0 + (size_t)expert * n_out * K;
     const W* e1 = DUAL ? w1 + (size_t)expert * n_out * K : nullptr;
@@ -276,8 +346,8 @@ moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w
     for (int i = 0; i < 4; ++i) {
         const int r = ty * 4 + i;
         if (r >= rows) continue;
-        const int pair = DUAL ? 0 : sorted_pairs[row0 + r];
-        const float scale = DUAL ? 1.f : pair_weight[pair];
+        const int pair = UP ? 0 : sorted_pairs[row0 + r];
+        const float scale = UP ? 1.f : pair_weight[pair];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
@@ -286,6 +356,8 @@ moe_expert_gemm_kernel(const T* __restrict__ A, int lda, const W* __restrict__ w
                 // the products are rounded to the activation type first, as a projection's output is
                 const float g = round_to<T>(acc0[i][j]), u = round_to<T>(acc1[i][j]);
                 hidden[(size_t)(row0 + r) * n_out + n] = from_f32<T>(expert_activation(kind, g, u, limit, alpha));
+            } else if (UP) {
+                hidden[(size_t)(row0 + r) * n_out + n] = from_f32<T>(expert_plain_activation(kind, round_to<T>(acc0[i][j])));
             } else {
                 y[(size_t)pair * n_out + n] = scale * acc0[i][j];
             }
@@ -317,13 +389,14 @@ __device__ __forceinline__ void moe_mma_bf16(float (&c)[4], const unsigned (&a)[
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool DUAL>
+template <int MODE>
 __global__ void __launch_bounds__(256)
 moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restrict__ w0, const bf16* __restrict__ w1,
                       const int* __restrict__ tiles, const int* __restrict__ info,
                       const int* __restrict__ sorted_pairs, int top, const float* __restrict__ pair_weight,
                       bf16* __restrict__ hidden, float* __restrict__ y, int n_out, int K, int kind, float limit,
                       float alpha) {
+    constexpr bool DUAL = MODE == 1, UP = MODE != 0;
     extern __shared__ __align__(16) unsigned char moe_smem[];
     typedef bf16 (*TileA)[MOE_BM][MOE_LDS];
     typedef bf16 (*TileB)[MOE_BN][MOE_LDS];
@@ -339,7 +412,7 @@ moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restric
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;      // this warp's 32 x 32 corner of the 128 x 64 tile
     const int n0 = blockIdx.x * MOE_BN;
-    if (tid < MOE_BM) src_row[tid] = tid < rows ? (DUAL ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
+    if (tid < MOE_BM) src_row[tid] = tid < rows ? (UP ? sorted_pairs[row0 + tid] / top : row0 + tid) : -1;
     __syncthreads();
     const bf16* e0 = w0 + (size_t)expert * n_out * K;
     const bf16* e1 = DUAL ? w1 + (size_t)expert * n_out * K : nullptr;
@@ -420,8 +493,8 @@ moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restric
         for (int half = 0; half < 2; ++half) {
             const int r = wm + m * 16 + (lane >> 2) + half * 8;
             if (r >= rows) continue;
-            const int pair = DUAL ? 0 : sorted_pairs[row0 + r];
-            const float scale = DUAL ? 1.f : pair_weight[pair];
+            const int pair = UP ? 0 : sorted_pairs[row0 + r];
+            const float scale = UP ? 1.f : pair_weight[pair];
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
@@ -431,6 +504,9 @@ moe_expert_mma_kernel(const bf16* __restrict__ A, int lda, const bf16* __restric
                     if (DUAL) {
                         const float g = round_to<bf16>(acc0[m][nt][half * 2 + e]), u = round_to<bf16>(acc1[m][nt][half * 2 + e]);
                         hidden[(size_t)(row0 + r) * n_out + n] = __float2bfloat16_rn(expert_activation(kind, g, u, limit, alpha));
+                    } else if (UP) {
+                        hidden[(size_t)(row0 + r) * n_out + n] =
+                            __float2bfloat16_rn(expert_plain_activation(kind, round_to<bf16>(acc0[m][nt][half * 2 + e])));
                     } else {
                         y[(size_t)pair * n_out + n] = scale * acc0[m][nt][half * 2 + e];
                     }
@@ -446,9 +522,10 @@ static int moe_mma_smem(bool dual) {
 static int moe_mma_configure() {
     static bool configured = false;
     if (configured) return 0;
-    cudaError_t a = cudaFuncSetAttribute(moe_expert_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_mma_smem(true));
-    cudaError_t b = cudaFuncSetAttribute(moe_expert_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_mma_smem(false));
-    if (a != cudaSuccess || b != cudaSuccess) QIL_REFUSE("moe: cannot reserve %d bytes of shared memory", moe_mma_smem(true));
+    cudaError_t a = cudaFuncSetAttribute(moe_expert_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_mma_smem(true));
+    cudaError_t b = cudaFuncSetAttribute(moe_expert_mma_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_mma_smem(false));
+    cudaError_t c = cudaFuncSetAttribute(moe_expert_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, moe_mma_smem(false));
+    if (a != cudaSuccess || b != cudaSuccess || c != cudaSuccess) QIL_REFUSE("moe: cannot reserve %d bytes of shared memory", moe_mma_smem(true));
     configured = true;
     return 0;
 }
@@ -460,31 +537,56 @@ static bool moe_tensor_cores_usable(int act_dtype, int weight_dtype, int lda, in
 }
 
 // ------------------------------------------------------------------ combine
-template <typename R>
+// What a combine may do beyond the sum: identity outputs of the router, an expert that every token uses, a scale.
+struct CombineExtras {
+    const int* chosen;         // with `x`: pairs whose choice is >= n_experts add weight * x instead of an expert's row
+    const float* weights;
+    const void* x;             // the experts' input rows, activation type
+    int n_experts;
+    const float* extra;        // float32 [N, width] or null: added times sigmoid(gate_logit[token])
+    const float* gate_logit;   // float32 [N] or null (no gate: extra is added as it is)
+    const float* col_scale;    // float32 [width] or null
+};
+
+template <typename R, typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ y, const R* __restrict__ residual, R* __restrict__ out, size_t total,
-                   int width, int top) {
+                   int width, int top, CombineExtras ex) {
     qil_wait_for_producer();
     qil_release_consumer();
+    const T* x = reinterpret_cast<const T*>(ex.x);
     for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256) {
         const size_t token = i / width;
         const int col = (int)(i % width);
         float sum = 0.f;
-        for (int s = 0; s < top; ++s) sum += y[(token * top + s) * width + col];
+        for (int s = 0; s < top; ++s) {
+            const size_t pair = token * top + s;
+            if (x != nullptr && ex.chosen[pair] >= ex.n_experts) sum += ex.weights[pair] * to_f32<T>(x[i]);
+            else sum += y[pair * width + col];
+        }
+        if (ex.extra != nullptr)
+            sum += (ex.gate_logit != nullptr ? 1.f / (1.f + expf(-ex.gate_logit[token])) : 1.f) * ex.extra[i];
+        if (ex.col_scale != nullptr) sum *= ex.col_scale[col];
         out[i] = from_f32<R>(residual != nullptr ? to_f32<R>(residual[i]) + sum : sum);
     }
 }
 
 // ------------------------------------------------------------------ entry points
+// `router` holds n_experts rows, and one more behind them when `gate_logit` is given.
 extern "C" int qil_moe_route(const void* x, const void* router, const void* bias, int n_tokens, int width,
-                             int n_experts, int top, int* chosen, float* weights, int act_dtype, int weight_dtype,
+                             int n_experts, int top, int* chosen, float* weights, int mode, const float* correction,
+                             float weight_scale, float* gate_logit, int act_dtype, int weight_dtype,
                              cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (n_experts <= 0 || n_experts > MOE_MAX_EXPERTS || top <= 0 || top > n_experts || top > MOE_MAX_TOP || width <= 0)
+    if (n_experts <= 0 || n_experts + (gate_logit != nullptr ? 1 : 0) > MOE_MAX_EXPERTS || top <= 0 || top > n_experts
+        || top > MOE_MAX_TOP || width <= 0)
         QIL_REFUSE("moe_route: %d experts (at most %d), %d of them per token, width %d", n_experts, MOE_MAX_EXPERTS, top, width);
+    if (mode != 0 && mode != 1) QIL_REFUSE("moe_route: mode %d", mode);
+    if (gate_logit != nullptr && bias != nullptr) QIL_REFUSE("moe_route: a gate row goes without router biases");
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         qil_launch_chained(moe_route_kernel<T, W>, dim3(n_tokens), dim3(256), 0, stream, (const T*)x, (const W*)router,
-                           (const W*)bias, width, n_experts, top, chosen, weights));
+                           (const W*)bias, width, n_experts, top, chosen, weights, mode, correction, weight_scale,
+                           gate_logit));
     QIL_CHECK_LAUNCH();
 }
 
@@ -515,18 +617,32 @@ extern "C" int qil_moe_gate_up(const void* x, int lda, const void* gate_w, const
     if (max_tiles <= 0) return 0;
     if (max_tiles > 65535) QIL_REFUSE("moe_gate_up: %d row tiles are too many for one launch", max_tiles);
     dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
-    if (moe_tensor_cores_usable(act_dtype, weight_dtype, lda, K, x, gate_w, up_w)) {
+    const bool gated = up_w != nullptr;        // without a second stack: h = act(A W^T), the activation has no gate
+    if (!gated && kind != 0 && kind != 1 && kind != 3) QIL_REFUSE("moe_gate_up: activation %d needs a gate matrix", kind);
+    if (gated && kind != 0 && kind != 2) QIL_REFUSE("moe_gate_up: activation %d takes no gate matrix", kind);
+    if (moe_tensor_cores_usable(act_dtype, weight_dtype, lda, K, x, gate_w, gated ? up_w : gate_w)) {
         if (moe_mma_configure()) return -1;
-        qil_launch_chained(moe_expert_mma_kernel<true>, grid, dim3(256), moe_mma_smem(true), stream, (const bf16*)x, lda,
-                           (const bf16*)gate_w, (const bf16*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
-                           (bf16*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha);
+        if (gated)
+            qil_launch_chained(moe_expert_mma_kernel<1>, grid, dim3(256), moe_mma_smem(true), stream, (const bf16*)x, lda,
+                               (const bf16*)gate_w, (const bf16*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
+                               (bf16*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha);
+        else
+            qil_launch_chained(moe_expert_mma_kernel<2>, grid, dim3(256), moe_mma_smem(false), stream, (const bf16*)x, lda,
+                               (const bf16*)gate_w, (const bf16*)nullptr, tiles, info, sorted_pairs, top, (const float*)nullptr,
+                               (bf16*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha);
         QIL_CHECK_LAUNCH();
     }
     grid.z = MOE_BM / MOE_FM;
-    QIL_DISPATCH_2(act_dtype, weight_dtype,
-        (qil_launch_chained(moe_expert_gemm_kernel<T, W, true>, grid, dim3(256), 0, stream, (const T*)x, lda,
-                            (const W*)gate_w, (const W*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
-                            (T*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha)));
+    if (gated)
+        QIL_DISPATCH_2(act_dtype, weight_dtype,
+            (qil_launch_chained(moe_expert_gemm_kernel<T, W, 1>, grid, dim3(256), 0, stream, (const T*)x, lda,
+                                (const W*)gate_w, (const W*)up_w, tiles, info, sorted_pairs, top, (const float*)nullptr,
+                                (T*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha)));
+    else
+        QIL_DISPATCH_2(act_dtype, weight_dtype,
+            (qil_launch_chained(moe_expert_gemm_kernel<T, W, 2>, grid, dim3(256), 0, stream, (const T*)x, lda,
+                                (const W*)gate_w, (const W*)nullptr, tiles, info, sorted_pairs, top, (const float*)nullptr,
+                                (T*)hidden, (float*)nullptr, n_out, K, kind, limit, alpha)));
     QIL_CHECK_LAUNCH();
 }
 
@@ -538,26 +654,31 @@ extern "C" int qil_moe_down(const void* hidden, const void* down_w, const int* t
     dim3 grid((n_out + MOE_BN - 1) / MOE_BN, max_tiles);
     if (moe_tensor_cores_usable(act_dtype, weight_dtype, K, K, hidden, down_w, down_w)) {
         if (moe_mma_configure()) return -1;
-        qil_launch_chained(moe_expert_mma_kernel<false>, grid, dim3(256), moe_mma_smem(false), stream, (const bf16*)hidden, K,
+        qil_launch_chained(moe_expert_mma_kernel<0>, grid, dim3(256), moe_mma_smem(false), stream, (const bf16*)hidden, K,
                            (const bf16*)down_w, (const bf16*)nullptr, tiles, info, sorted_pairs, 1, pair_weight,
                            (bf16*)nullptr, y, n_out, K, 0, 0.f, 0.f);
         QIL_CHECK_LAUNCH();
     }
     grid.z = MOE_BM / MOE_FM;
     QIL_DISPATCH_2(act_dtype, weight_dtype,
-        (qil_launch_chained(moe_expert_gemm_kernel<T, W, false>, grid, dim3(256), 0, stream, (const T*)hidden, K,
+        (qil_launch_chained(moe_expert_gemm_kernel<T, W, 0>, grid, dim3(256), 0, stream, (const T*)hidden, K,
                             (const W*)down_w, (const W*)nullptr, tiles, info, sorted_pairs, 1, pair_weight,
                             (T*)nullptr, y, n_out, K, 0, 0.f, 0.f)));
     QIL_CHECK_LAUNCH();
 }
 
 extern "C" int qil_moe_combine(const float* y, const void* residual, void* out, int n_tokens, int width, int top,
-                               int stream_dtype, cudaStream_t stream) {
+                               int stream_dtype, const int* chosen, const float* weights, const void* x, int x_dtype,
+                               int n_experts, const float* extra, const float* gate_logit, const float* col_scale,
+                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (x != nullptr && (chosen == nullptr || weights == nullptr)) QIL_REFUSE("moe_combine: identity outputs need the choice and the weights");
     const size_t total = (size_t)n_tokens * width;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    QIL_DISPATCH_1(stream_dtype,
-        qil_launch_chained(moe_combine_kernel<T>, dim3(blocks), dim3(256), 0, stream, y, (const T*)residual, (T*)out,
-                           total, width, top));
+    CombineExtras ex = {chosen, weights, x, n_experts, extra, gate_logit, col_scale};
+    // R: the stream's type, T: the input rows' type
+    QIL_DISPATCH_2(x_dtype, stream_dtype,
+        qil_launch_chained(moe_combine_kernel<W, T>, dim3(blocks), dim3(256), 0, stream, y, (const W*)residual, (W*)out,
+                           total, width, top, ex));
     QIL_CHECK_LAUNCH();
 }

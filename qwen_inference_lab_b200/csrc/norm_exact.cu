@@ -54,3 +54,100 @@ extern "C" int qil_rmsnorm_exact(const void* x, int x_dtype, const void* weight,
 #undef QIL_NORM_GO
     QIL_CHECK_LAUNCH();
 }
+
+// Layer norm with weight and bias, float32 from end to end like the norm above:
+//
+//   y = (x - mean) / sqrt(var + eps) * w + b,     var = mean((x - mean)^2)
+//
+// Two passes over the row (the mean, then the squared deviations from it), each a fixed tree.
+template <typename TI, typename TO, typename W>
+__global__ void __launch_bounds__(256)
+layernorm_exact_kernel(const TI* __restrict__ x, const W* __restrict__ weight, const W* __restrict__ bias,
+                       const int* __restrict__ rows, TO* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[32];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const int r = blockIdx.x;
+    const TI* src = x + (size_t)(rows ? rows[r] : r) * width;
+    TO* dst = out + (size_t)r * width;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) sum += to_f32<TI>(src[i]);
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = to_f32<TI>(src[i]) - mean;
+        sq = fmaf(v, v, sq);
+    }
+    sq = block_sum(sq, scratch);
+    const float scale = 1.0f / sqrtf(sq / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += 256)
+        dst[i] = from_f32<TO>((to_f32<TI>(src[i]) - mean) * scale * to_f32<W>(weight[i]) + to_f32<W>(bias[i]));
+}
+
+extern "C" int qil_layernorm_exact(const void* x, int x_dtype, const void* weight, const void* bias, int weight_dtype,
+                                   const int* rows, void* out, int out_dtype, int n_rows, int width, float eps,
+                                   cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0) QIL_REFUSE("layernorm_exact: width %d", width);
+#define QIL_NORM_GO(TI, TO)                                                                                    \
+    do {                                                                                                       \
+        if (weight_dtype == QIL_F32)                                                                           \
+            qil_launch_chained(layernorm_exact_kernel<TI, TO, float>, dim3(n_rows), dim3(256), 0, stream,      \
+                               (const TI*)x, (const float*)weight, (const float*)bias, rows, (TO*)out, width, eps); \
+        else                                                                                                   \
+            qil_launch_chained(layernorm_exact_kernel<TI, TO, bf16>, dim3(n_rows), dim3(256), 0, stream,       \
+                               (const TI*)x, (const bf16*)weight, (const bf16*)bias, rows, (TO*)out, width, eps); \
+    } while (0)
+    if (weight_dtype != QIL_F32 && weight_dtype != QIL_BF16) QIL_REFUSE("layernorm_exact: weight dtype %d", weight_dtype);
+    if (x_dtype == QIL_F32 && out_dtype == QIL_F32) QIL_NORM_GO(float, float);
+    else if (x_dtype == QIL_F32 && out_dtype == QIL_BF16) QIL_NORM_GO(float, bf16);
+    else if (x_dtype == QIL_BF16 && out_dtype == QIL_BF16) QIL_NORM_GO(bf16, bf16);
+    else if (x_dtype == QIL_BF16 && out_dtype == QIL_F32) QIL_NORM_GO(bf16, float);
+    else QIL_REFUSE("layernorm_exact: dtypes %d -> %d", x_dtype, out_dtype);
+#undef QIL_NORM_GO
+    QIL_CHECK_LAUNCH();
+}
+
+// x += y / sqrt(mean(y^2) + eps) * w: a branch that is normed by its own root mean square before it joins the
+// residual stream.  float32 arithmetic; x is the stream (float32 or bfloat16), y the branch.
+template <typename TX, typename TY, typename W>
+__global__ void __launch_bounds__(256)
+rms_scale_add_kernel(TX* __restrict__ x, const TY* __restrict__ y, const W* __restrict__ weight, int width, float eps) {
+    __shared__ float scratch[32];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const TY* src = y + (size_t)blockIdx.x * width;
+    TX* dst = x + (size_t)blockIdx.x * width;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = to_f32<TY>(src[i]);
+        sq = fmaf(v, v, sq);
+    }
+    sq = block_sum(sq, scratch);
+    const float scale = 1.0f / sqrtf(sq / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += 256)
+        dst[i] = from_f32<TX>(to_f32<TX>(dst[i]) + to_f32<TY>(src[i]) * scale * to_f32<W>(weight[i]));
+}
+
+extern "C" int qil_rms_scale_add(void* x, int x_dtype, const void* y, int y_dtype, const void* weight, int weight_dtype,
+                                 int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width <= 0) QIL_REFUSE("rms_scale_add: width %d", width);
+#define QIL_NORM_GO(TX, TY)                                                                                   \
+    do {                                                                                                      \
+        if (weight_dtype == QIL_F32)                                                                          \
+            qil_launch_chained(rms_scale_add_kernel<TX, TY, float>, dim3(n_rows), dim3(256), 0, stream,       \
+                               (TX*)x, (const TY*)y, (const float*)weight, width, eps);                       \
+        else                                                                                                  \
+            qil_launch_chained(rms_scale_add_kernel<TX, TY, bf16>, dim3(n_rows), dim3(256), 0, stream,        \
+                               (TX*)x, (const TY*)y, (const bf16*)weight, width, eps);                        \
+    } while (0)
+    if (weight_dtype != QIL_F32 && weight_dtype != QIL_BF16) QIL_REFUSE("rms_scale_add: weight dtype %d", weight_dtype);
+    if (x_dtype == QIL_F32 && y_dtype == QIL_F32) QIL_NORM_GO(float, float);
+    else if (x_dtype == QIL_F32 && y_dtype == QIL_BF16) QIL_NORM_GO(float, bf16);
+    else if (x_dtype == QIL_BF16 && y_dtype == QIL_BF16) QIL_NORM_GO(bf16, bf16);
+    else if (x_dtype == QIL_BF16 && y_dtype == QIL_F32) QIL_NORM_GO(bf16, float);
+    else QIL_REFUSE("rms_scale_add: dtypes %d += %d", x_dtype, y_dtype);
+#undef QIL_NORM_GO
+    QIL_CHECK_LAUNCH();
+}

@@ -17,7 +17,8 @@ F32, BF16 = 0, 1
 _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "gemm_small_m.cu", "attention_generic.cu",
-                "sampling.cu", "norm_exact.cu", "gated_activation.cu", "qkv_store.cu", "gla_scan.cu", "moe.cu"]
+                "sampling.cu", "norm_exact.cu", "gated_activation.cu", "qkv_store.cu", "gla_scan.cu", "moe.cu",
+                "short_conv.cu"]
 SMALL_M_MAX_ROWS = min(16, tuning.SMALL_M_MAX_ROWS)      # the kernel takes 16 at most
 
 _core = None
@@ -290,11 +291,11 @@ def cast(src, dtype, out=None):
     return out
 
 
-def gemm_f32(a, weight, bias=None, residual=None, out=None):
-    """out = a @ weight.T (+ bias) (+ residual), float32 accumulation on the CUDA cores.
+def gemm_f32(a, weight, bias=None, residual=None, out=None, col_scale=None):
+    """out = (a @ weight.T (+ bias)) (* col_scale) (+ residual), float32 accumulation on the CUDA cores.
 
     a [M,K] and out [M,N] share a dtype; weight [N,K] and bias [N] share another.
-    ``residual`` may be ``out`` itself.
+    ``residual`` may be ``out`` itself.  ``col_scale`` float32 [N]: a scale per output feature.
     """
     _need(a, "a", ndim=2); _need(weight, "weight", ndim=2)
     m, k = a.shape
@@ -314,9 +315,14 @@ def gemm_f32(a, weight, bias=None, residual=None, out=None):
         _need(residual, "residual", a.dtype, 2)
         if residual.shape != (m, n):
             raise KernelError("gemm_f32: residual has the wrong shape")
+    if col_scale is not None:
+        _need(col_scale, "col_scale", torch.float32, 1)
+        if col_scale.shape[0] != n:
+            raise KernelError("gemm_f32: col_scale has the wrong length")
     lib = core()
     _check(lib, lib.qil_gemm_f32(_p(a), c_int(k), _p(weight), _p(bias), _p(residual), _p(out), c_int(m), c_int(n),
-                                 c_int(k), c_int(dtype_code(a.dtype)), c_int(dtype_code(weight.dtype)), _stream()),
+                                 c_int(k), c_int(dtype_code(a.dtype)), c_int(dtype_code(weight.dtype)), _p(col_scale),
+                                 _stream()),
            "gemm_f32")
     return out
 
@@ -375,11 +381,15 @@ def check_pages(kv_cache, dtype, n_kv_heads, page_size, head_dim, v_dim, what):
 
 
 def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_heads, n_kv_heads,
-                      head_dim, page_size, window, scale, v_dim=None, slopes=None):
+                      head_dim, page_size, window, scale, v_dim=None, slopes=None, softcap=0.0, distance_bias=None,
+                      chunk=0, sink=False):
     """Causal GQA attention of every token over its request's pages (CUDA cores, float32 math).
 
     ``v_dim``: the size of a value head when it differs from ``head_dim`` (out is then [N, Hq * v_dim]).
-    ``slopes`` float32 [Hq]: score = q.k * scale - slopes[h] * (query position - key position)."""
+    ``slopes`` float32 [Hq]: score = q.k * scale - slopes[h] * (query position - key position).
+    ``softcap``: score <- softcap * tanh(score / softcap) before any bias.  ``distance_bias`` float32
+    [Hq, distances]: added by distance, the last entry for every distance beyond.  ``chunk``: a position sees
+    only the keys of its own chunk of that many positions.  ``sink``: one is added to the softmax's denominator."""
     v_dim = head_dim if v_dim is None else int(v_dim)
     _need(q, "q", ndim=2); _need(out, "out", q.dtype, 2)
     check_pages(kv_cache, q.dtype, n_kv_heads, page_size, head_dim, v_dim, "attention_generic")
@@ -390,13 +400,19 @@ def attention_generic(q, kv_cache, out, positions, token_row, block_table, n_q_h
         _need(slopes, "slopes", torch.float32, 1)
         if slopes.shape[0] != n_q_heads:
             raise KernelError("attention_generic: one slope per query head")
+    if distance_bias is not None:
+        _need(distance_bias, "distance_bias", torch.float32, 2)
+        if distance_bias.shape[0] != n_q_heads or distance_bias.shape[1] < 1:
+            raise KernelError("attention_generic: the distance table is [query heads, distances]")
     _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
     _need(block_table, "block_table", torch.int32, 2)
     lib = core()
     _check(lib, lib.qil_attention_generic(
         _p(q), _p(kv_cache), _p(out), _p(positions), _p(token_row), _p(block_table), c_int(block_table.shape[1]),
         c_int(n), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_dim), c_int(page_size),
-        c_int(kv_cache.shape[0]), c_int(window), c_float(scale), _p(slopes), c_int(dtype_code(q.dtype)), _stream()),
+        c_int(kv_cache.shape[0]), c_int(window), c_float(scale), _p(slopes), c_float(softcap), _p(distance_bias),
+        c_int(distance_bias.shape[1] if distance_bias is not None else 0), c_int(chunk), c_int(1 if sink else 0),
+        c_int(dtype_code(q.dtype)), _stream()),
         "attention_generic")
     return out
 
@@ -423,7 +439,113 @@ def rmsnorm_exact(x, weight, eps, offset=0.0, out_dtype=None, rows=None, out=Non
     return out
 
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+def layernorm_exact(x, weight, bias, eps, out_dtype=None, rows=None, out=None):
+    """y = (x - mean) / sqrt(var + eps) * weight + bias with float32 arithmetic and one rounding; var is the mean
+    of the squared deviations.  ``x`` float32 or bfloat16 [N, width]; the result has ``out_dtype`` (default: x's)."""
+    _need(x, "x", ndim=2); _need(weight, "weight", ndim=1); _need(bias, "bias", weight.dtype, 1)
+    width = x.shape[1]
+    if weight.shape[0] != width or bias.shape[0] != width:
+        raise KernelError(f"layernorm_exact: weight of {weight.shape[0]}, bias of {bias.shape[0]} for width {width}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+    n_rows = x.shape[0] if rows is None else rows.shape[0]
+    if out is None:
+        out = torch.empty((n_rows, width), dtype=out_dtype or x.dtype, device=x.device)
+    _need(out, "out", ndim=2)
+    if out.shape != (n_rows, width):
+        raise KernelError("layernorm_exact: out has the wrong shape")
+    lib = core()
+    _check(lib, lib.qil_layernorm_exact(_p(x), c_int(dtype_code(x.dtype)), _p(weight), _p(bias),
+                                        c_int(dtype_code(weight.dtype)), _p(rows), _p(out), c_int(dtype_code(out.dtype)),
+                                        c_int(n_rows), c_int(width), c_float(eps), _stream()), "layernorm_exact")
+    return out
+
+
+def rms_scale_add(x, y, weight, eps):
+    """x += y / sqrt(mean(y^2) + eps) * weight, row by row, float32 arithmetic: a branch normed by its own root
+    mean square joins the stream ``x`` (float32 or bfloat16 [N, width]) in place."""
+    _need(x, "x", ndim=2); _need(y, "y", ndim=2); _need(weight, "weight", ndim=1)
+    if y.shape != x.shape or weight.shape[0] != x.shape[1]:
+        raise KernelError("rms_scale_add: shapes differ")
+    lib = core()
+    _check(lib, lib.qil_rms_scale_add(_p(x), c_int(dtype_code(x.dtype)), _p(y), c_int(dtype_code(y.dtype)), _p(weight),
+                                      c_int(dtype_code(weight.dtype)), c_int(x.shape[0]), c_int(x.shape[1]), c_float(eps),
+                                      _stream()), "rms_scale_add")
+    return x
+
+
+def scaled_add(x, y, scale):
+    """x[r, c] += scale[c] * y[r, c] in place (float32 arithmetic); ``scale`` float32 [width]."""
+    _need(x, "x", ndim=2); _need(y, "y", ndim=2); _need(scale, "scale", torch.float32, 1)
+    if y.shape != x.shape or scale.shape[0] != x.shape[1]:
+        raise KernelError("scaled_add: shapes differ")
+    lib = core()
+    _check(lib, lib.qil_scaled_add(_p(x), c_int(dtype_code(x.dtype)), _p(y), c_int(dtype_code(y.dtype)), _p(scale),
+                                   c_int(x.shape[0]), c_int(x.shape[1]), _stream()), "scaled_add")
+    return x
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2, "relu2": 3}
+PLAIN_ACTIVATIONS = ("silu", "gelu_tanh", "relu2")      # those that need no gate
+
+
+def activation(z, kind, *, table=None, ids=None, first_col=0, out=None):
+    """out = act(z) for ``kind`` in ``PLAIN_ACTIVATIONS`` (``relu2``: max(z, 0)^2); with ``table`` [rows, columns]
+    and ``ids`` int32 [N]: out[r, c] = act(z[r, c]) * table[ids[r], first_col + c].  ``out`` may be ``z``."""
+    _need(z, "z", ndim=2)
+    if kind not in PLAIN_ACTIVATIONS:
+        raise KernelError(f"activation: unknown kind {kind!r} (known: {PLAIN_ACTIVATIONS})")
+    if out is None:
+        out = torch.empty_like(z)
+    _need(out, "out", z.dtype, 2)
+    if table is not None:
+        _need(table, "table", ndim=2); _need(ids, "ids", torch.int32, 1)
+        if ids.shape[0] != z.shape[0] or first_col < 0 or first_col + z.shape[1] > table.shape[1]:
+            raise KernelError("activation: the table's columns or the ids do not fit the rows")
+    lib = core()
+    _check(lib, lib.qil_activation(_p(z), _p(out), c_int(z.shape[0]), c_int(z.shape[1]), c_int(dtype_code(z.dtype)),
+                                   c_int(ACTIVATIONS[kind]), _p(table),
+                                   c_int(dtype_code(table.dtype) if table is not None else 0), _p(ids),
+                                   c_int(table.shape[1] if table is not None else 0), c_int(first_col),
+                                   c_int(table.shape[0] if table is not None else 0), _stream()), "activation")
+    return out
+
+
+def short_conv_store(u, taps_weight, state, q_out, kv_cache, positions, token_row, block_table, seg_row, seg_start,
+                     seg_len, n_segments, n_q_heads, n_kv_heads, head_dim, v_dim, page_size):
+    """A short causal convolution over time on every channel of ``u`` [N, Hq*d + Hkv*d + Hkv*e] (the stacked q/k/v
+    projection), queries to ``q_out``, keys and values into the pages.  ``taps_weight`` [channels, taps];
+    ``state`` float32 [slots, taps - 1, channels]: the last rows of ``u`` that each request has seen, read for
+    the positions before a step's first token and moved on.  Segments are the step's (int32 device arrays)."""
+    _need(u, "u", ndim=2); _need(q_out, "q_out", u.dtype, 2); _need(taps_weight, "taps_weight", ndim=2)
+    n, channels = u.shape
+    taps = taps_weight.shape[1]
+    if channels != n_q_heads * head_dim + n_kv_heads * (head_dim + v_dim) or q_out.shape != (n, n_q_heads * head_dim) \
+            or taps_weight.shape[0] != channels:
+        raise KernelError("short_conv_store: shapes do not match the head counts")
+    _need(state, "state", torch.float32, 3)
+    if tuple(state.shape[1:]) != (taps - 1, channels):
+        raise KernelError(f"short_conv_store: state {tuple(state.shape)} for {taps} taps and {channels} channels")
+    _need(positions, "positions", torch.int32, 1); _need(token_row, "token_row", torch.int32, 1)
+    num_pages = 0
+    if n_kv_heads:
+        check_pages(kv_cache, u.dtype, n_kv_heads, page_size, head_dim, v_dim, "short_conv_store")
+        _need(block_table, "block_table", torch.int32, 2)
+        num_pages = kv_cache.shape[0]
+    lib = core()
+    _check(lib, lib.qil_short_conv_store(
+        _p(u), _p(taps_weight), _p(state), _p(q_out), _p(kv_cache if n_kv_heads else None), _p(positions),
+        _p(token_row), _p(block_table if n_kv_heads else None), c_int(block_table.shape[1] if n_kv_heads else 0),
+        c_int(n), c_int(taps), c_int(n_q_heads), c_int(n_kv_heads), c_int(head_dim), c_int(v_dim), c_int(page_size),
+        c_int(num_pages), c_int(dtype_code(u.dtype)), c_int(dtype_code(taps_weight.dtype)), _stream()),
+        "short_conv_store")
+    if taps > 1 and n_segments < n:      # some request brought more than one token: its state moves on here
+        for t in (seg_row, seg_start, seg_len):
+            _need(t, "segments", torch.int32, 1)
+        _check(lib, lib.qil_short_conv_state(_p(u), _p(state), _p(seg_row), _p(seg_start), _p(seg_len), c_int(n_segments),
+                                             c_int(taps), c_int(channels), c_int(dtype_code(u.dtype)), _stream()),
+               "short_conv_state")
+    return q_out
 
 
 def gated_activation(gate_up, kind, *, limit=0.0, alpha=1.0, pairs8=False, out=None):
@@ -574,39 +696,66 @@ def gla_norm_gate(scratch, projected, gate_column, norm_weight, eps, n_heads, e,
     return out
 
 
-def moe_route(x, router, bias, top):
+def moe_route(x, router, bias, top, *, softmax_all=False, correction=None, weight_scale=1.0, gate_row=False):
     """(chosen int32 [N, top], weights float32 [N, top]): the ``top`` largest of x R^T + b per row (float32
-    arithmetic; the lower index wins a tie) and the softmax over those logits alone."""
+    arithmetic; the lower index wins a tie) and the softmax over those logits alone.
+
+    ``softmax_all``: scores are the softmax over all outputs; the choice goes by score + ``correction`` (float32
+    [outputs]), the weights are the chosen scores divided by their sum (+ 1e-20), times ``weight_scale``.
+    ``gate_row``: the last row of ``router`` is not an output but a gate's weights: its dot products are returned
+    as a third result, float32 [N]."""
     _need(x, "x", ndim=2); _need(router, "router", ndim=2)
     if router.shape[1] != x.shape[1]:
         raise KernelError("moe_route: the router's width differs from x's")
     if bias is not None:
         _need(bias, "bias", router.dtype, 1)
     n = x.shape[0]
+    outputs = router.shape[0] - (1 if gate_row else 0)
+    if correction is not None:
+        _need(correction, "correction", torch.float32, 1)
+        if correction.shape[0] != outputs:
+            raise KernelError("moe_route: one correction per output of the router")
     chosen = torch.empty((n, top), dtype=torch.int32, device=x.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    gate = torch.empty((n,), dtype=torch.float32, device=x.device) if gate_row else None
     lib = core()
-    _check(lib, lib.qil_moe_route(_p(x), _p(router), _p(bias), c_int(n), c_int(x.shape[1]), c_int(router.shape[0]),
-                                  c_int(top), _p(chosen), _p(weights), c_int(dtype_code(x.dtype)),
+    _check(lib, lib.qil_moe_route(_p(x), _p(router), _p(bias), c_int(n), c_int(x.shape[1]), c_int(outputs),
+                                  c_int(top), _p(chosen), _p(weights), c_int(1 if softmax_all else 0), _p(correction),
+                                  c_float(weight_scale), _p(gate), c_int(dtype_code(x.dtype)),
                                   c_int(dtype_code(router.dtype)), _stream()), "moe_route")
-    return chosen, weights
+    return (chosen, weights, gate) if gate_row else (chosen, weights)
 
 
-def moe_experts(x, chosen, weights, gate_w, up_w, down_w, kind, *, limit=0.0, alpha=1.0, residual=None, out=None):
+def moe_experts(x, chosen, weights, gate_w, up_w, down_w, kind, *, limit=0.0, alpha=1.0, residual=None, out=None,
+                identity=False, extra=None, extra_gate=None, col_scale=None):
     """out = residual + sum over a token's chosen experts of weight * down_e(act(gate_e x, up_e x)).
 
     gate_w, up_w [E, ff, width]; down_w [E, width, ff]; ``kind`` as in ``gated_activation`` (``silu`` or
-    ``clamped_swish``).  ``residual`` and ``out`` [N, width] share a dtype (the residual stream's)."""
+    ``clamped_swish``).  ``residual`` and ``out`` [N, width] share a dtype (the residual stream's).
+    ``up_w`` None: experts without a gate matrix, down_e(act(gate_w_e x)) with ``kind`` in ``PLAIN_ACTIVATIONS``.
+    ``identity``: a choice >= E names no expert and adds weight * x.  ``extra`` float32 [N, width]: added too,
+    times sigmoid(``extra_gate``) (float32 [N]) when that is given.  ``col_scale`` float32 [width] multiplies
+    everything that is added to the residual."""
     _need(x, "x", ndim=2); _need(chosen, "chosen", torch.int32, 2); _need(weights, "weights", torch.float32, 2)
-    _need(gate_w, "gate_w", ndim=3); _need(up_w, "up_w", gate_w.dtype, 3); _need(down_w, "down_w", gate_w.dtype, 3)
+    _need(gate_w, "gate_w", ndim=3); _need(down_w, "down_w", gate_w.dtype, 3)
+    if up_w is not None:
+        _need(up_w, "up_w", gate_w.dtype, 3)
     n, width = x.shape
     experts, ff, _ = gate_w.shape
     top = chosen.shape[1]
-    if (gate_w.shape != (experts, ff, width) or up_w.shape != gate_w.shape or down_w.shape != (experts, width, ff)
-            or chosen.shape[0] != n or weights.shape != chosen.shape):
+    if (gate_w.shape != (experts, ff, width) or (up_w is not None and up_w.shape != gate_w.shape)
+            or down_w.shape != (experts, width, ff) or chosen.shape[0] != n or weights.shape != chosen.shape):
         raise KernelError("moe_experts: shapes do not fit together")
-    if kind not in ("silu", "clamped_swish"):
+    if kind not in (("silu", "clamped_swish") if up_w is not None else PLAIN_ACTIVATIONS):
         raise KernelError(f"moe_experts: activation {kind!r}")
+    if extra is not None:
+        _need(extra, "extra", torch.float32, 2)
+        if extra.shape != (n, width):
+            raise KernelError("moe_experts: extra has the wrong shape")
+    if extra_gate is not None:
+        _need(extra_gate, "extra_gate", torch.float32, 1)
+    if col_scale is not None:
+        _need(col_scale, "col_scale", torch.float32, 1)
     stream_dtype = residual.dtype if residual is not None else (out.dtype if out is not None else x.dtype)
     if out is None:
         out = torch.empty((n, width), dtype=stream_dtype, device=x.device)
@@ -631,7 +780,9 @@ def moe_experts(x, chosen, weights, gate_w, up_w, down_w, kind, *, limit=0.0, al
     _check(lib, lib.qil_moe_down(_p(hidden), _p(down_w), _p(tiles), _p(info), c_int(max_tiles), _p(sorted_pairs),
                                  _p(weights), _p(y), c_int(width), c_int(ff), act, wt, _stream()), "moe_down")
     _check(lib, lib.qil_moe_combine(_p(y), _p(residual), _p(out), c_int(n), c_int(width), c_int(top),
-                                    c_int(dtype_code(stream_dtype)), _stream()), "moe_combine")
+                                    c_int(dtype_code(stream_dtype)), _p(chosen), _p(weights), _p(x if identity else None),
+                                    c_int(dtype_code(x.dtype)), c_int(experts), _p(extra), _p(extra_gate), _p(col_scale),
+                                    _stream()), "moe_combine")
     return out
 
 

@@ -1,3 +1,4 @@
 """Importing this package registers every architecture the engine knows."""
 from . import qwen3  # noqa: F401
 from . import virulix  # noqa: F401
+from . import debisun  # noqa: F401

@@ -2,11 +2,12 @@
 from .base import (FeedForward, KVCacheSpec, Mixer, Norm, Param, Part, PlanView, PositionEncoding, Segments,
                    StateSpec, StepContext, StepPlanner)
 from .linear import Linear, StackedLinear
-from .norm import ExactRMSNorm, RMSNorm
+from .norm import ExactRMSNorm, LayerNorm, RMSNorm
 from .rotary import RotaryEmbedding, rotary_table
 from .attention import GroupedQueryAttention
-from .feed_forward import GatedMLP
+from .feed_forward import GatedMLP, PlainMLP
 from .experts import RoutedExperts
 from .linear_attention import GatedLinearAttention
 from .block import PreNormBlock
+from .side_input import TokenSideInput
 from .decoder import DecoderModel, LayerCall, TokenEmbedding

@@ -12,14 +12,26 @@ Options for designs without rotation: a bias that grows with distance taken off 
 (``distance_slopes``, one slope per query head: score = q.k * scale - slope_h * (i - j)), a query
 temperature that grows with the logarithm of the position (``q_temperature`` = (coef, every):
 q_p * (1 + coef * ln(floor((p + 1) / every) + 1))), and value heads of another size than key heads
-(``v_head_dim``).
+(``v_head_dim``).  Further options, each with its constants as arguments:
+
+``conv_taps``      a short causal convolution over time on every channel of q, k and v right after the
+                   projection (weights ``<q|k|v><conv suffix>`` [channels, taps]); the last taps - 1 projected rows
+                   of a request are kept in a state slot beside its pages
+``softcap``        score <- cap * tanh(score / cap) on the scaled product, before any bias
+``distance_bias``  (rows, farthest): a learned table [rows, query heads] (``names["distance_bias"]``) added to the
+                   score by distance: one row per distance below rows / 2, then rows that grow with the logarithm
+                   of the distance up to ``farthest``, the last row for everything beyond (``distance_rows``)
+``chunk``          position i sees the keys j <= i of its own chunk only: floor(i / chunk) = floor(j / chunk)
+``sink``           one is added to the softmax's denominator (a key of score zero without a value)
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
 from ..kernels import attention_mma, gemm_tc, ops
-from .base import KVCacheSpec, Mixer, Param, StepPlanner
+from .base import KVCacheSpec, Mixer, Param, StateSpec, StepPlanner
 from .linear import Linear, StackedLinear
 
 
@@ -40,6 +52,21 @@ class PagedAttentionPlanner(StepPlanner):
 _PLANNER = PagedAttentionPlanner()
 
 
+def distance_rows(rows: int, farthest: int, count: int) -> list:
+    """The row of a distance table with ``rows`` rows for each distance 0 .. count - 1: the distance itself below
+    half = rows // 2, else min(rows - 1, half + floor(ln(n / half) / ln(farthest / half) * (rows - half)))."""
+    half = rows // 2
+    if rows < 2 or farthest <= half:
+        raise ValueError(f"a distance table of {rows} rows needs a farthest distance beyond {half}, not {farthest}")
+    result = []
+    for n in range(count):
+        if n < half:
+            result.append(n)
+        else:
+            result.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(farthest / half) * (rows - half)))))
+    return result
+
+
 class GroupedQueryAttention(Mixer):
     """Sizes and constants are arguments; ``names`` gives the checkpoint names.
 
@@ -53,7 +80,8 @@ class GroupedQueryAttention(Mixer):
     def __init__(self, hidden_size, n_q_heads, n_kv_heads, head_dim, *, names, bias=False,
                  qk_norm_eps=None, position=None, window=0, scale=None, reads_shared_cache=False,
                  v_head_dim=None, distance_slopes=None, q_temperature=None, out_bias=None,
-                 suffixes=(".weight", ".bias")):
+                 suffixes=(".weight", ".bias"), conv_taps=0, conv_suffix=".conv", softcap=0.0, distance_bias=None,
+                 chunk=0, sink=False):
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads do not divide into {n_kv_heads} kv heads")
         self.hidden_size, self.head_dim = int(hidden_size), int(head_dim)
@@ -70,9 +98,18 @@ class GroupedQueryAttention(Mixer):
         self.q_temperature = None if not q_temperature else (float(q_temperature[0]), int(q_temperature[1]))
         if self.q_temperature is not None and self.q_temperature[1] < 1:
             raise ValueError("the query temperature's step must be a positive number of positions")
+        self.conv_taps, self.softcap, self.chunk, self.sink = int(conv_taps), float(softcap or 0.0), int(chunk or 0), bool(sink)
+        if self.conv_taps < 0 or self.softcap < 0 or self.chunk < 0:
+            raise ValueError("taps, softcap and chunk size cannot be negative")
+        self.distance_bias = None if not distance_bias else (int(distance_bias[0]), int(distance_bias[1]))
+        self.modified_scores = bool(self.softcap or self.distance_bias or self.chunk or self.sink)
+        if self.modified_scores and self.window:
+            raise ValueError("a window does not go with chunks, a softcap, a distance table or a sink")
         # without per-head norms and rotation the projection's tail is a copy (times the temperature) and the page write
         self.plain_tail = (self.v_head_dim != self.head_dim or self.distance_slopes is not None
-                           or self.q_temperature is not None)
+                           or self.q_temperature is not None or self.conv_taps > 0 or self.modified_scores)
+        if self.conv_taps and self.q_temperature is not None:
+            raise ValueError("the short convolution goes without a query temperature")
         if self.plain_tail and (qk_norm_eps is not None or position is not None):
             raise ValueError("distance slopes, query temperature and a value size of its own go without q/k norms and rotation")
         self._slopes = self._slopes_log2 = None
@@ -82,6 +119,18 @@ class GroupedQueryAttention(Mixer):
         self.qkv = StackedLinear(hidden_size, pieces, bias=bias, suffixes=suffixes)
         self.out = Linear(n_q_heads * self.v_head_dim, hidden_size, name=names["o"],
                           bias=bias if out_bias is None else out_bias, suffixes=suffixes)
+        self._extra = {}
+        self.conv = None
+        if self.conv_taps:
+            self.conv = [Param((rows, self.conv_taps), std=0.5) for _, rows in pieces]
+            for (name, _), param in zip(pieces, self.conv):
+                self._extra[name + suffixes[0] + conv_suffix] = param
+        self.distance_table = None
+        if self.distance_bias is not None:
+            distance_rows(self.distance_bias[0], self.distance_bias[1], 1)      # refuses constants that do not fit
+            self.distance_table = Param((self.distance_bias[0], self.n_q_heads), std=0.5)
+            self._extra[names["distance_bias"]] = self.distance_table
+        self._conv_w = self._bias_by_distance = None
         self.q_norm = self.k_norm = None
         self._norm_names = None
         if qk_norm_eps is not None:
@@ -91,8 +140,8 @@ class GroupedQueryAttention(Mixer):
 
     def named_params(self):
         if self._norm_names is None:
-            return {}
-        return {self._norm_names[0]: self.q_norm, self._norm_names[1]: self.k_norm}
+            return dict(self._extra)
+        return {self._norm_names[0]: self.q_norm, self._norm_names[1]: self.k_norm, **self._extra}
 
     def children(self):
         parts = [self.qkv, self.out]
@@ -107,32 +156,70 @@ class GroupedQueryAttention(Mixer):
         if self.distance_slopes is not None:
             self._slopes = torch.tensor(self.distance_slopes, dtype=torch.float32, device=device)
             self._slopes_log2 = (self._slopes.double() * 1.4426950408889634).float().contiguous()
+        if self.conv is not None:
+            self._conv_w = torch.cat([p.data for p in self.conv], dim=0).contiguous()
+            for p in self.conv:
+                p.data = None
+        if self.distance_table is not None:
+            # the table by distance, one row per query head: the kernels look a distance up, not a bucket; every
+            # distance from the first one of the last row on reads the last entry, and a chunk bounds the distances
+            rows, farthest = self.distance_bias
+            of_distance = distance_rows(rows, farthest, farthest + 1)
+            count = of_distance.index(rows - 1) + 1
+            if self.chunk:
+                count = max(1, min(count, self.chunk))
+            index = torch.tensor(of_distance[:count], dtype=torch.long, device=self.distance_table.data.device)
+            self._bias_by_distance = self.distance_table.data.float()[index].t().contiguous()
 
     def step_planners(self):
         return {**super().step_planners(), _PLANNER.key: _PLANNER}
 
     def cache_spec(self):
-        if self.reads_shared_cache:
-            return None
-        return KVCacheSpec(self.n_kv_heads, self.head_dim, self.window,
-                           self.v_head_dim if self.v_head_dim != self.head_dim else 0)
+        """Pages for keys and values; with a short convolution also a state slot for the projected rows that the
+        next step's first tokens reach back to (a pair of specs: the view is then a pair too)."""
+        pages = None if self.reads_shared_cache else KVCacheSpec(
+            self.n_kv_heads, self.head_dim, self.window, self.v_head_dim if self.v_head_dim != self.head_dim else 0,
+            chunk=self.chunk)
+        if self.conv_taps > 1:
+            if self.reads_shared_cache:
+                raise ValueError("a layer with a short convolution keeps keys and values of its own")
+            return (pages, StateSpec((self.conv_taps - 1, self.qkv.out_features), torch.float32))
+        return pages
 
     takes_norm = True
 
-    def forward(self, ctx, x, cache, residual=None, norm=None):
-        """x [N, hidden] -> [N, hidden] (+ residual).  ``cache`` is a KVCacheView.  With ``norm`` x is
-        the block's un-normed input and the first projection applies the norm."""
+    @property
+    def takes_out_scale(self):
+        return self.plain_tail
+
+    def forward(self, ctx, x, cache, residual=None, norm=None, out_scale=None):
+        """x [N, hidden] -> [N, hidden] (+ residual).  ``cache`` is a KVCacheView (with a short convolution: a
+        pair of it and a StateView).  With ``norm`` x is the block's un-normed input and the first projection
+        applies the norm."""
         n = x.shape[0]
         n_kv = 0 if self.reads_shared_cache else self.n_kv_heads
         if self.plain_tail:
             qkv = self.qkv.forward(ctx, x, norm=norm)
             q = ctx.empty((n, self.n_q_heads * self.head_dim))
-            coef, every = self.q_temperature or (0.0, 0)
-            ops.qkv_store(qkv, q, cache.pages, ctx.positions, ctx.token_row, cache.block_table, self.n_q_heads, n_kv,
-                          self.head_dim, self.v_head_dim, cache.page_size, coef, every)
+            if self.conv_taps:
+                state = None
+                if self.conv_taps > 1:
+                    cache, state = cache
+                    state = state.slots
+                else:
+                    state = torch.empty((1, 0, qkv.shape[1]), dtype=torch.float32, device=qkv.device)
+                ops.short_conv_store(qkv, self._conv_w, state, q, cache.pages, ctx.positions, ctx.token_row,
+                                     cache.block_table, ctx.seg_row, ctx.seg_start, ctx.seg_len, ctx.n_segments,
+                                     self.n_q_heads, n_kv, self.head_dim, self.v_head_dim, cache.page_size)
+            else:
+                coef, every = self.q_temperature or (0.0, 0)
+                ops.qkv_store(qkv, q, cache.pages, ctx.positions, ctx.token_row, cache.block_table, self.n_q_heads,
+                              n_kv, self.head_dim, self.v_head_dim, cache.page_size, coef, every)
             attended = ctx.empty((n, self.n_q_heads * self.v_head_dim))
             self._attend(ctx, q, cache, attended)
-            return self.out.forward(ctx, attended, residual=residual)
+            return self.out.forward(ctx, attended, residual=residual, out_scale=out_scale)
+        if out_scale is not None:
+            raise ValueError("an output scale is taken by the layers without q/k norms and rotation only")
         table = self.position.table if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         q_norm = self.q_norm.data if self.q_norm is not None else None
@@ -166,6 +253,13 @@ class GroupedQueryAttention(Mixer):
         return self.out.forward(ctx, attended, residual=residual)
 
     def _attend(self, ctx, q, cache, out):
+        if self.modified_scores:
+            ops.attention_generic(q, cache.pages, out, ctx.positions, ctx.token_row, cache.block_table,
+                                  self.n_q_heads, self.n_kv_heads, self.head_dim, cache.page_size,
+                                  self.window, self.scale, v_dim=self.v_head_dim, slopes=self._slopes,
+                                  softcap=self.softcap, distance_bias=self._bias_by_distance, chunk=self.chunk,
+                                  sink=self.sink)
+            return
         if q.dtype == torch.bfloat16 and self.v_head_dim == self.head_dim \
                 and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads):
             attention_mma.attend(ctx, q, cache, out, self.n_q_heads, self.n_kv_heads, self.head_dim,

@@ -65,11 +65,14 @@ class KVCacheSpec:
     ``window`` > 0 means that only the last ``window`` positions are ever read, so
     pages that the window has passed are given back while the request lives.
     ``v_head_dim``: the size of a value head where it differs from a key head's (0: the same).
+    ``chunk`` > 0 means that a position reads only the positions of its own chunk of that many
+    (chunks counted from position 0), so pages of chunks that are over are given back as well.
     """
     kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
+    chunk: int = 0
 
     @property
     def value_dim(self) -> int:

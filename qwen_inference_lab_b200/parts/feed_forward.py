@@ -1,4 +1,5 @@
-"""Gated feed-forward: ``down(silu(gate(x)) * up(x))`` (qil/model.py:38-40,70-71).
+"""Feed-forwards: the gated ``down(silu(gate(x)) * up(x))`` (qil/model.py:38-40,70-71) and the plain
+``down(act(up(x)))`` of designs without a gate matrix (:class:`PlainMLP`).
 
 gate and up are one stacked product; the activation rounds ``silu(gate)`` to the
 activation dtype before the multiply, as elementwise tensor code does.  In
@@ -74,3 +75,29 @@ class GatedMLP(FeedForward):
             gate_up = self.gate_up.forward(ctx, x)
             hidden = ops.silu_mul(gate_up, pairs8=self.pairs8)
         return self.down.forward(ctx, hidden, residual=residual)
+
+
+class PlainMLP(FeedForward):
+    """``down(act(up x))`` without a gate matrix; ``activation`` is one of ``ops.PLAIN_ACTIVATIONS`` (``relu2``: the
+    square of relu).  names: dict with keys up, down.  The up product, an activation kernel, the down product
+    (with the residual, and a learned scale per feature on the way into it, in its last kernel)."""
+    graph_safe = True
+    takes_norm = True
+    takes_out_scale = True
+
+    def __init__(self, hidden_size, intermediate_size, *, names, activation="relu2", bias=False,
+                 suffixes=(".weight", ".bias")):
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        if activation not in ops.PLAIN_ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r} (known: {ops.PLAIN_ACTIVATIONS})")
+        self.activation = activation
+        self.up = Linear(hidden_size, intermediate_size, name=names["up"], bias=bias, suffixes=suffixes)
+        self.down = Linear(intermediate_size, hidden_size, name=names["down"], bias=bias, suffixes=suffixes)
+
+    def children(self):
+        return [self.up, self.down]
+
+    def forward(self, ctx, x, residual=None, norm=None, out_scale=None, out_float32=False):
+        hidden = self.up.forward(ctx, x, norm=norm)
+        ops.activation(hidden, self.activation, out=hidden)
+        return self.down.forward(ctx, hidden, residual=residual, out_scale=out_scale, out_float32=out_float32)

@@ -55,14 +55,28 @@ class Linear(Part):
     def _bias(self):
         return self.bias.data if self.bias is not None else None
 
-    def forward(self, ctx, x, residual=None, out=None, out_float32=False, norm=None):
+    def forward(self, ctx, x, residual=None, out=None, out_float32=False, norm=None, out_scale=None):
         """``x`` [N, in] -> [N, out]; adds ``residual`` [N, out] when given (may be ``out``).
+
+        ``out_scale`` float32 [out]: a learned scale per output feature on the way into the residual, which is
+        then updated in place: residual += out_scale * (x W^T + b).
 
         With ``norm`` (a Norm part) the product is of ``norm(x)``: fused into the kernel where it can be.
         A float32 ``residual`` under bfloat16 activations (a residual stream kept in float32) gives a
         float32 result: the product's float32 sums are added to it without a rounding in between.
         """
         weight, bias = self._weight(), self._bias()
+        if out_scale is not None:
+            if residual is None or out is not None:
+                raise ValueError("an output scale goes with a residual, which is updated in place")
+            if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+                branch = self.forward(ctx, x, out_float32=residual.dtype == torch.float32, norm=norm)
+                return ops.scaled_add(residual, branch, out_scale)
+            if norm is not None:
+                x = norm.forward(ctx, x)
+            if residual.dtype != x.dtype:
+                return ops.scaled_add(residual, ops.gemm_f32(x, weight, bias=bias), out_scale)
+            return ops.gemm_f32(x, weight, bias=bias, residual=residual, out=residual, col_scale=out_scale)
         if residual is not None and residual.dtype == torch.float32 and x.dtype == torch.bfloat16 \
                 and weight.dtype == torch.bfloat16:
             if norm is not None:

@@ -1,4 +1,4 @@
-"""Root-mean-square norm over the last dimension.
+"""Norms over the last dimension: root-mean-square norms and a layer norm.
 
 ``y = cast(x32 * rsqrt(mean(x32^2) + eps)) * w``: statistics and scaling in float32,
 rounded to the activation dtype, then multiplied by the weight (no ``1 + w``), as the
@@ -47,3 +47,25 @@ class ExactRMSNorm(Norm):
 
     def forward(self, ctx, x, rows=None):
         return ops.rmsnorm_exact(x, self.weight.data, self.eps, self.offset, out_dtype=ctx.dtype, rows=rows)
+
+
+class LayerNorm(Norm):
+    """``y = (x - mean) / sqrt(var + eps) * w + b`` with ``var`` the mean of the squared deviations: float32
+    arithmetic and a single rounding, like :class:`ExactRMSNorm`, and like it it may read a float32 residual
+    stream under bfloat16 activations.  ``suffixes``: what the checkpoint appends to ``name`` for weight and bias."""
+    graph_safe = True
+
+    def __init__(self, width, eps, *, name, suffixes=(".weight", ".bias"), optional=False):
+        self.width, self.eps, self.name, self.suffixes = int(width), float(eps), name, tuple(suffixes)
+        self.weight = Param((width,), init="norm", std=0.05, optional=optional)
+        self.bias = Param((width,), init="normal", std=0.05, optional=optional)
+
+    def named_params(self):
+        return {self.name + self.suffixes[0]: self.weight, self.name + self.suffixes[1]: self.bias}
+
+    def finalize(self, device, dtype):
+        if self.weight.data is not None and self.bias.data.dtype != self.weight.data.dtype:
+            self.bias.data = self.bias.data.to(self.weight.data.dtype)
+
+    def forward(self, ctx, x, rows=None):
+        return ops.layernorm_exact(x, self.weight.data, self.bias.data, self.eps, out_dtype=ctx.dtype, rows=rows)
