@@ -29,7 +29,7 @@ def build_parser():
     parser.add_argument("--max-tokens", required=True, type=int,
                         help="most tokens live requests hold at any time (each rounded up to 64)")
     parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (divides 64)")
-    parser.add_argument("--max-live", type=int, default=8, help="most requests alive at once")
+    parser.add_argument("--max-live", type=int, default=4, help="most requests alive at once (state slots)")
     return parser
 
 

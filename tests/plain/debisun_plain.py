@@ -124,6 +124,19 @@ def route(h, w, prefix, router):
     return chosen, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20) * router["scale"]
 
 
+def route_margin(h, w, prefix, router):
+    """Per token, how far the last chosen output's choice score lies above the best one that was not chosen, as a
+    fraction of the larger of the two outputs' scores (infinite when every output is chosen).  Rounding moves a
+    score by a fraction of itself, so a small value here is a close call that rounding can flip."""
+    scores = torch.softmax(h @ w[prefix + "router"].to(h.dtype).t(), dim=-1)
+    order = (scores + w[prefix + "correction"].to(h.dtype)).sort(dim=-1, descending=True)
+    top = router["top"]
+    if top >= scores.shape[1]:
+        return torch.full((h.shape[0],), float("inf"), dtype=h.dtype)
+    raw = torch.gather(scores, 1, order.indices[:, top - 1:top + 1]).max(dim=-1).values
+    return (order.values[:, top - 1] - order.values[:, top]) / raw.clamp(min=1e-30)
+
+
 def moe_ff(h, w, prefix, mlp, low=None):
     """Routed experts (the last ``identity`` of the router's outputs hand the input through), plus the shared
     expert times a sigmoid gate of one number per token."""
@@ -152,8 +165,9 @@ def token_side(x, tokens, w, prefix, index, dim, eps, low=None):
     return rms_norm(linear(g, w[prefix + "side.proj"], low), w[prefix + "side.norm"], eps)
 
 
-def forward(config, w, tokens, dtype=torch.float64, low=None, return_layers=False):
-    """Logits [T, vocab] of a whole sequence (and the residual stream after every layer)."""
+def forward(config, w, tokens, dtype=torch.float64, low=None, return_layers=False, margins=None):
+    """Logits [T, vocab] of a whole sequence (and the residual stream after every layer).  ``margins``: a list
+    that receives every routed layer's ``route_margin`` per token."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     eps = config["norm"]["eps"]
     side = config.get("token_side")
@@ -167,6 +181,8 @@ def forward(config, w, tokens, dtype=torch.float64, low=None, return_layers=Fals
         if mlp is not None:
             h = _round(layer_norm(x, w[p + "norm2"], w[p + "norm2.b"], eps), low)
             y = dense_ff(h, w, p + "mlp.", low) if mlp["kind"] == "dense" else moe_ff(h, w, p + "mlp.", mlp, low)
+            if margins is not None and mlp["kind"] == "moe":
+                margins.append(route_margin(h, w, p + "mlp.", mlp["router"]))
             x = x + y * w[p + "ls2"].to(dtype)
         if side:
             x = x + token_side(x, tokens, w, p, i, side["dim"], eps, low)
