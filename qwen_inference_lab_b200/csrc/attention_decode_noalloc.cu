@@ -48,7 +48,7 @@ static int noalloc_setup(int smem, float** scratch, unsigned** tickets) {
         noalloc_scratch_address[device] = address;
         noalloc_tickets_address[device] = counters;
     }
-    if (ensure_decode_smem(attn_decode_span_kernel, smem)) return -1;
+    if (ensure_decode_smem(attn_decode_span_kernel<false>, smem)) return -1;
     *scratch = noalloc_scratch_address[device];
     *tickets = noalloc_tickets_address[device];
     return 0;
@@ -89,7 +89,7 @@ extern "C" int qil_attn_decode_noalloc(const void* q, const void* kv, void* out,
     float* part_ml = scratch + o_floats;
     cudaError_t cleared = cudaMemsetAsync(tickets, 0, (size_t)n_tickets * sizeof(unsigned), stream);
     if (cleared != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(cleared)); return (int)cleared; }
-    attn_decode_span_kernel<<<dim3(n_kv_heads * chunks, n_decode, n_spans), 128, smem, stream>>>(
+    attn_decode_span_kernel<false><<<dim3(n_kv_heads * chunks, n_decode, n_spans), 128, smem, stream>>>(
         p, (const int4*)decode_info, part_o, part_ml, tickets, n_spans, span_len, DecodeTail{});
     QIL_CHECK_LAUNCH();
 }

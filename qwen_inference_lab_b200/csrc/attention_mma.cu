@@ -96,7 +96,30 @@ struct AttnParams {
     float scale_log2;         // head_dim^-1/2 * log2(e)
     // null, or one slope per query head, times log2(e): score = q.k * scale - slope_h * (query position - key position)
     const float* slopes_log2;
+    // Options that the MOD forms of the kernels apply (all float32, the score in natural units until the end):
+    //   softcap > 0   score <- softcap * tanh(q.k * scale / softcap), before any bias
+    //   dist_bias     float32 [Hq][dist_len]: added by distance (query position - key position), the last entry for
+    //                 every distance beyond the table
+    //   chunk > 0     a query sees only the keys of its own chunk of that many positions (counted from position 0)
+    //   sink          one is added to the softmax's denominator (a key of score 0 without a value)
+    float scale, softcap;
+    const float* dist_bias;
+    int dist_len, chunk, sink;
 };
+
+// tanh from one exponential: absolute error of a few 1e-7, which the cap multiplies.
+__device__ __forceinline__ float tanh_from_exp(float x) {
+    return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f);
+}
+
+// The modified score in units of log2: cap, distance table, slope.  `bias_row` is the query head's row of the table.
+__device__ __forceinline__ float modified_score_log2(const AttnParams& p, float dot, int distance, float slope_log2,
+                                                     const float* __restrict__ bias_row) {
+    float score = dot * p.scale;
+    if (p.softcap > 0.f) score = p.softcap * tanh_from_exp(score / p.softcap);
+    if (bias_row != nullptr) score += __ldg(bias_row + min(distance, p.dist_len - 1));
+    return fmaf(-(float)distance, slope_log2, score * 1.4426950408889634f);
+}
 
 // Where the key row of position ``pos`` of one kv head starts, in units of 16 bytes from the layer's
 // base (the value row lies one (kv_heads * page_size * D) plane further); -1 when the position is outside
@@ -129,6 +152,7 @@ __device__ __forceinline__ void issue_kv_tile(const AttnParams& p, const int* ro
 }
 
 // ------------------------------------------------------------------ prompt portions
+template <bool MOD>
 __global__ void __launch_bounds__(128, (QIL_HEAD_DIM <= 128) ? 3 : 1)
 attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -145,9 +169,11 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     const int4 info = tile_info[blockIdx.y];
     const int n0 = info.x, pos0 = info.y, rows = min(Q_TILE, info.z);
     const int hi = pos0 + rows - 1;
-    const int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
+    if (MOD && p.chunk > 0) lo = max(lo, pos0 / p.chunk * p.chunk);       // the first row's chunk: later rows see no more
     const int* table = p.block_table + (size_t)info.w * p.table_stride;
     const float slope = p.slopes_log2 != nullptr ? p.slopes_log2[head] : 0.f;
+    const float* bias_row = (MOD && p.dist_bias != nullptr) ? p.dist_bias + (size_t)head * p.dist_len : nullptr;
 
     {   // queries of this tile: two threads per row
         const int row = tid >> 1, half = tid & 1;
@@ -187,6 +213,8 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
     const int pos_a = pos0 + row_a, pos_b = pos0 + row_b;
+    const int lo_a = (MOD && p.chunk > 0) ? pos_a / p.chunk * p.chunk : 0;     // where each row's own chunk begins
+    const int lo_b = (MOD && p.chunk > 0) ? pos_b / p.chunk * p.chunk : 0;
 
     for (int tile = first_tile; tile <= last_tile; ++tile) {
         const int buf = (tile - first_tile) & 1;
@@ -225,8 +253,21 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
         // scale, mask by absolute position, online softmax (float32).  A tile that lies wholly at or before
         // the first row's position and inside the last row's window needs no mask.
         float tmax_a = -INFINITY, tmax_b = -INFINITY;
-        const bool full = (tile + 1) * KV_TILE - 1 <= pos0 && (p.window == 0 || tile * KV_TILE > hi - p.window);
-        if (full && slope == 0.f) {
+        const bool full = !MOD && (tile + 1) * KV_TILE - 1 <= pos0 && (p.window == 0 || tile * KV_TILE > hi - p.window);
+        if (MOD) {
+#pragma unroll
+            for (int nt = 0; nt < KV_TILE / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = tile * KV_TILE + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = (e < 2) ? pos_a : pos_b;
+                    const bool ok = key <= pos && key >= ((e < 2) ? lo_a : lo_b) && (p.window == 0 || key > pos - p.window);
+                    const float v = ok ? modified_score_log2(p, s[nt][e], pos - key, slope, bias_row) : -INFINITY;
+                    s[nt][e] = v;
+                    if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
+                }
+            }
+        } else if (full && slope == 0.f) {
 #pragma unroll
             for (int nt = 0; nt < KV_TILE / 8; ++nt) {
 #pragma unroll
@@ -288,6 +329,10 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     }
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (MOD && p.sink) {      // the sink's weight: exp2(0 - max) beside the keys' sums (one when no key was seen)
+        l_a += (m_a == -INFINITY) ? 1.f : exp2f(-m_a);
+        l_b += (m_b == -INFINITY) ? 1.f : exp2f(-m_b);
+    }
     const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt) {
@@ -453,6 +498,7 @@ __device__ __forceinline__ void merge_spans_of_head(const AttnParams& p, const f
         }
         mx = new_max;
     }
+    if (p.sink) sum += (mx == -INFINITY) ? 1.f : exp2f(-mx);
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
 #pragma unroll
     for (int i = 0; i < COLS; ++i) {
@@ -471,7 +517,7 @@ __device__ __forceinline__ void merge_spans_of_head(const AttnParams& p, const f
 // so that a kernel that walks several such places in a loop can call it too.  ``wait_for_inputs`` is called once,
 // after the first key and value tiles have been asked for: up to there only memory that nothing of this step
 // writes is read.
-template <typename Wait>
+template <bool MOD, typename Wait>
 __device__ __forceinline__ void attn_decode_span_block(
         const AttnParams& p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
         float* __restrict__ part_ml, unsigned* __restrict__ tickets, int n_spans, int span_len_arg,
@@ -497,7 +543,15 @@ __device__ __forceinline__ void attn_decode_span_block(
     const int4 info = decode_info[d_idx];
     const int n = info.x, pos = info.y;
     const int hi = pos;
-    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    if (p.chunk > 0 && pos >= 0) lo = max(lo, pos / p.chunk * p.chunk);
+    const float* bias_a = nullptr;            // the rows of the distance table of this lane's two query heads
+    const float* bias_b = nullptr;
+    if (MOD && p.dist_bias != nullptr) {
+        const int row = (threadIdx.x & 31) >> 2;
+        if (row < gcount) bias_a = p.dist_bias + (size_t)(kv_head * group + g0 + row) * p.dist_len;
+        if (row + 8 < gcount) bias_b = p.dist_bias + (size_t)(kv_head * group + g0 + row + 8) * p.dist_len;
+    }
     const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
     const int k_begin = span * span_len;
     if (k_begin > hi || k_begin + span_len <= lo) return;    // takes no ticket: the merge counts the same spans
@@ -635,7 +689,11 @@ __device__ __forceinline__ void attn_decode_span_block(
             for (int e = 0; e < 4; ++e) {
                 const int key = tile * KV_TILE + warp * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
                 const bool ok = key <= hi && key >= lo;
-                s[nt][e] = ok ? fmaf((float)(key - hi), e < 2 ? slope_a : slope_b, s[nt][e] * p.scale_log2) : -INFINITY;
+                if (MOD)
+                    s[nt][e] = ok ? modified_score_log2(p, s[nt][e], hi - key, e < 2 ? slope_a : slope_b, e < 2 ? bias_a : bias_b)
+                                  : -INFINITY;
+                else
+                    s[nt][e] = ok ? fmaf((float)(key - hi), e < 2 ? slope_a : slope_b, s[nt][e] * p.scale_log2) : -INFINITY;
             }
         }
         float tmax_a = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -717,6 +775,7 @@ __device__ __forceinline__ void attn_decode_span_block(
         }
         const int head = kv_head * group + g0 + r;
         if (alone) {
+            if (p.sink) sum += (mx == -INFINITY) ? 1.f : exp2f(-mx);
             const float inv = sum > 0.f ? 1.f / sum : 0.f;
             p.out[((size_t)n * p.n_q_heads + head) * D + col] =
                 __float2bfloat16_rn(uncovered ? __int_as_float(0x7fc00000) : acc * inv);
@@ -755,7 +814,8 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
     const int d_idx = blockIdx.y, head = blockIdx.x * 4 + (threadIdx.x >> 5);
     const int4 info = decode_info[d_idx];
     const int pos = info.y;
-    const int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    int lo = (p.window > 0 && pos - p.window + 1 > 0) ? pos - p.window + 1 : 0;
+    if (p.chunk > 0 && pos >= 0) lo = max(lo, pos / p.chunk * p.chunk);
     const int span_len = span_len_arg > 0 ? span_len_arg : span_len_of(info.w, n_spans, -span_len_arg);
     const int s_lo = lo / span_len;
     int s_hi = pos / span_len;
@@ -768,13 +828,14 @@ attn_decode_merge_kernel(AttnParams p, const int4* __restrict__ decode_info, con
         merge_spans_of_head(p, part_o, part_ml, d_idx, info.x, head, n_spans, s_lo, s_hi, uncovered, threadIdx.x & 31);
 }
 
+template <bool MOD>
 __global__ void __launch_bounds__(128)
 attn_decode_span_kernel(AttnParams p, const int4* __restrict__ decode_info, float* __restrict__ part_o,
                         float* __restrict__ part_ml, unsigned* __restrict__ tickets, int n_spans, int span_len_arg,
                         DecodeTail tail) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // the span index varies slowest: see span_len_of
-    attn_decode_span_block(p, decode_info, part_o, part_ml, tickets, n_spans, span_len_arg, tail, smem_raw,
+    attn_decode_span_block<MOD>(p, decode_info, part_o, part_ml, tickets, n_spans, span_len_arg, tail, smem_raw,
                            (int)blockIdx.x, (int)gridDim.x, (int)blockIdx.y, (int)blockIdx.z,
                            [] { qil_wait_for_producer(); qil_release_consumer(); });
 }
@@ -795,7 +856,21 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes_log2 = nullptr;
+    p.scale = scale; p.softcap = 0.f; p.dist_bias = nullptr; p.dist_len = 0; p.chunk = 0; p.sink = 0;
     return 0;
+}
+
+// The options of the MOD kernels, checked; returns whether any is set.
+static int fill_options(AttnParams& p, float softcap, const float* dist_bias, int dist_len, int chunk, int sink) {
+    if (softcap < 0.f || chunk < 0 || (dist_bias != nullptr && dist_len < 1))
+        QIL_REFUSE("attention: softcap %g chunk %d distance table of %d", softcap, chunk, dist_len);
+    if ((softcap > 0.f || dist_bias != nullptr || chunk > 0 || sink) && p.window > 0)
+        QIL_REFUSE("attention: a window does not go with chunks, a softcap, a distance table or a sink");
+    p.softcap = softcap; p.dist_bias = dist_bias; p.dist_len = dist_len; p.chunk = chunk; p.sink = sink ? 1 : 0;
+    return 0;
+}
+static bool has_options(const AttnParams& p) {
+    return p.softcap > 0.f || p.dist_bias != nullptr || p.chunk > 0 || p.sink != 0;
 }
 
 // Shared memory of the span kernel: query rows, two stages of key and value tiles (reused for the
@@ -809,17 +884,17 @@ static int decode_smem_bytes(int span_len, int page_size) {
 // that launches the kernel goes through here, so the limit is only ever raised.  One slot per device
 // ordinal; not safe for host threads that call these entry points at the same time.
 #define QIL_ATTN_MAX_DEVICES 64
-static int decode_smem_configured[QIL_ATTN_MAX_DEVICES];
+static int decode_smem_configured[2][QIL_ATTN_MAX_DEVICES];      // [plain, MOD]
 template <typename Kernel>
-static int ensure_decode_smem(Kernel kernel, int smem) {
+static int ensure_decode_smem(Kernel kernel, int smem, int variant = 0) {
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) QIL_REFUSE("attention: cudaGetDevice: %s", cudaGetErrorString(e));
     if (device < 0 || device >= QIL_ATTN_MAX_DEVICES) QIL_REFUSE("attention: device %d is out of range", device);
-    if (smem > decode_smem_configured[device]) {
+    if (smem > decode_smem_configured[variant][device]) {
         e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
-        decode_smem_configured[device] = smem;
+        decode_smem_configured[variant][device] = smem;
     }
     return 0;
 }
@@ -837,26 +912,49 @@ extern "C" int qil_attn_max_decode_span() { return MAX_DECODE_SPAN; }
 
 // tile_info: int32 [n_tiles, 4] = (first token, its absolute position, rows <= 64, block-table row).
 // slopes_log2: null, or float32 [n_q_heads]: a distance bias per query head (see AttnParams).
-extern "C" int qil_attn_prefill_biased(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
-                                       const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
-                                       int page_size, int num_pages, int window, float scale,
-                                       const float* slopes_log2, cudaStream_t stream) {
+static int launch_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                          int page_size, int num_pages, int window, float scale,
+                          const float* slopes_log2, float softcap, const float* dist_bias, int dist_len, int chunk,
+                          int sink, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     p.slopes_log2 = slopes_log2;
+    if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink)) return -1;
     if (n_tiles > 65535) QIL_REFUSE("attention: %d query tiles in one launch; at most 65535", n_tiles);
     if ((uintptr_t)tile_info & 15) QIL_REFUSE("attention: tile_info must be 16-byte aligned");
     const int smem = ((Q_IN_REGS ? 0 : Q_TILE) + 4 * KV_TILE) * LDS * (int)sizeof(bf16);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    attn_prefill_kernel<<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
+    if (has_options(p)) attn_prefill_kernel<true><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
+    else attn_prefill_kernel<false><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
+}
+
+extern "C" int qil_attn_prefill_biased(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                       const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                       int page_size, int num_pages, int window, float scale,
+                                       const float* slopes_log2, cudaStream_t stream) {
+    return launch_prefill(q, kv, out, tile_info, n_tiles, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
+                          num_pages, window, scale, slopes_log2, 0.f, nullptr, 0, 0, 0, stream);
+}
+
+// The same with the options of the MOD kernels (see AttnParams): softcap, a distance table float32
+// [n_q_heads][dist_len], chunks, a sink.
+extern "C" int qil_attn_prefill_modified(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
+                                         const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                         int page_size, int num_pages, float scale, const float* slopes_log2,
+                                         float softcap, const float* dist_bias, int dist_len, int chunk, int sink,
+                                         cudaStream_t stream) {
+    return launch_prefill(q, kv, out, tile_info, n_tiles, block_table, table_stride, n_q_heads, n_kv_heads, page_size,
+                          num_pages, 0, scale, slopes_log2, softcap, dist_bias, dist_len, chunk, sink, stream);
 }
 
 extern "C" int qil_attn_prefill(const void* q, const void* kv, void* out, const int* tile_info, int n_tiles,
@@ -879,21 +977,29 @@ static int launch_decode(const void* q, const void* kv, void* out, const int* de
                          float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
                          const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
                          int page_size, int num_pages, int window, float scale, const DecodeTail& tail,
-                         cudaStream_t stream, const float* slopes_log2 = nullptr) {
+                         cudaStream_t stream, const float* slopes_log2 = nullptr, float softcap = 0.f,
+                         const float* dist_bias = nullptr, int dist_len = 0, int chunk = 0, int sink = 0) {
     if (n_decode <= 0) return 0;
     AttnParams p;
     if (fill_params(p, q, kv, out, block_table, table_stride, n_q_heads, n_kv_heads, page_size, num_pages,
                     window, scale)) return -1;
     p.slopes_log2 = slopes_log2;
+    if (fill_options(p, softcap, dist_bias, dist_len, chunk, sink)) return -1;
     if (check_decode_span(span_len, n_spans)) return -1;
     if (part_o == nullptr || part_ml == nullptr) QIL_REFUSE("attention: decode needs scratch for %d spans", n_spans);
     if ((uintptr_t)decode_info & 15) QIL_REFUSE("attention: decode_info must be 16-byte aligned");
     const int chunks = (n_q_heads / n_kv_heads + 15) / 16;
     if (n_decode > 65535 || n_spans > 65535) QIL_REFUSE("attention: grid too large");
     const int smem = decode_smem_bytes(span_len > 0 ? span_len : -span_len, page_size);
-    if (ensure_decode_smem(attn_decode_span_kernel, smem)) return -1;
-    qil_launch_chained(attn_decode_span_kernel, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
-                       p, (const int4*)decode_info, part_o, part_ml, tickets, n_spans, span_len, tail);
+    if (has_options(p)) {
+        if (ensure_decode_smem(attn_decode_span_kernel<true>, smem, 1)) return -1;
+        qil_launch_chained(attn_decode_span_kernel<true>, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
+                           p, (const int4*)decode_info, part_o, part_ml, tickets, n_spans, span_len, tail);
+    } else {
+        if (ensure_decode_smem(attn_decode_span_kernel<false>, smem, 0)) return -1;
+        qil_launch_chained(attn_decode_span_kernel<false>, dim3(n_kv_heads * chunks, n_decode, n_spans), dim3(128), smem, stream,
+                           p, (const int4*)decode_info, part_o, part_ml, tickets, n_spans, span_len, tail);
+    }
     if (tickets == nullptr) {
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) { snprintf(qil_error_text, sizeof(qil_error_text), "%s", cudaGetErrorString(e)); return (int)e; }
@@ -921,6 +1027,19 @@ extern "C" int qil_attn_decode_biased(const void* q, const void* kv, void* out, 
     DecodeTail none = {};
     return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
                          table_stride, n_q_heads, n_kv_heads, page_size, num_pages, window, scale, none, stream, slopes_log2);
+}
+
+// The same with the options of the MOD kernels (see AttnParams).
+extern "C" int qil_attn_decode_modified(const void* q, const void* kv, void* out, const int* decode_info, int n_decode,
+                                        float* part_o, float* part_ml, unsigned* tickets, int n_spans, int span_len,
+                                        const int* block_table, int table_stride, int n_q_heads, int n_kv_heads,
+                                        int page_size, int num_pages, float scale, const float* slopes_log2,
+                                        float softcap, const float* dist_bias, int dist_len, int chunk, int sink,
+                                        cudaStream_t stream) {
+    DecodeTail none = {};
+    return launch_decode(q, kv, out, decode_info, n_decode, part_o, part_ml, tickets, n_spans, span_len, block_table,
+                         table_stride, n_q_heads, n_kv_heads, page_size, num_pages, 0, scale, none, stream, slopes_log2,
+                         softcap, dist_bias, dist_len, chunk, sink);
 }
 
 // The same over the raw output of the query/key/value projection, for steps in which every token is a single

@@ -193,13 +193,46 @@ def _check_slopes(slopes_log2, n_q_heads):
         raise KernelError("attention: the distance slopes must be float32 [query heads] on the device")
 
 
+class ScoreOptions:
+    """What a design does to its scores beyond scale and causal mask, for the kernels that take it:
+    ``softcap`` (score <- cap * tanh(score / cap) before any bias), ``distance_bias`` (float32 [Hq, distances] on
+    the device, added by distance, the last entry for every distance beyond), ``chunk`` (a position sees the keys
+    of its own chunk of that many positions only), ``sink`` (one added to the softmax's denominator)."""
+
+    def __init__(self, softcap=0.0, distance_bias=None, chunk=0, sink=False):
+        self.softcap, self.distance_bias, self.chunk, self.sink = float(softcap or 0.0), distance_bias, int(chunk or 0), bool(sink)
+
+    def __bool__(self):
+        return bool(self.softcap or self.distance_bias is not None or self.chunk or self.sink)
+
+    def check(self, n_q_heads):
+        bias = self.distance_bias
+        if bias is not None and (bias.dtype != torch.float32 or bias.ndim != 2 or bias.shape[0] != n_q_heads
+                                 or not bias.is_cuda or not bias.is_contiguous()):
+            raise KernelError("attention: the distance table must be float32 [query heads, distances] on the device")
+
+    def arguments(self):
+        bias = self.distance_bias
+        return (c_float(self.softcap), _p(bias), c_int(bias.shape[1] if bias is not None else 0), c_int(self.chunk),
+                c_int(1 if self.sink else 0))
+
+
 def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_heads, head_dim, page_size, window,
-            scale, slopes_log2=None):
+            scale, slopes_log2=None, options=None):
     """tile_info int32 [n_tiles * 4]: (first token, its position, rows <= 64, block-table row) per tile.
     ``slopes_log2`` float32 [Hq]: slope_h * log2(e) of a bias slope_h * (query position - key position) that is
-    taken off the scaled score."""
+    taken off the scaled score.  ``options``: a :class:`ScoreOptions` (no window then)."""
     lib = library(head_dim)
     _check_slopes(slopes_log2, n_q_heads)
+    if options:
+        options.check(n_q_heads)
+        if window:
+            raise KernelError("attention: score options go without a window")
+        _check(lib, lib.qil_attn_prefill_modified(
+            _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
+            c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_float(scale),
+            _p(slopes_log2), *options.arguments(), _stream()), "attention (prompt portions)")
+        return
     _check(lib, lib.qil_attn_prefill_biased(
         _p(q), _p(pages), _p(out), _p(tile_info), c_int(n_tiles), _p(block_table), c_int(block_table.shape[1]),
         c_int(n_q_heads), c_int(n_kv_heads), c_int(page_size), c_int(pages.shape[0]), c_int(window),
@@ -207,7 +240,7 @@ def prefill(q, pages, out, tile_info, n_tiles, block_table, n_q_heads, n_kv_head
 
 
 def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_len, block_table,
-           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None, slopes_log2=None):
+           n_q_heads, n_kv_heads, head_dim, page_size, window, scale, tickets=None, slopes_log2=None, options=None):
     """decode_info int32 [n_decode * 4]: (token, its position, block-table row, the step's longest context)
     per single token.  A negative ``span_len``: the kernels cut the step's longest context into ``n_spans``
     equal spans of at most ``-span_len`` positions (see ``plan_spans``).  ``tickets``: int32 zeros, one per
@@ -215,6 +248,16 @@ def decode(q, pages, out, decode_info, n_decode, part_o, part_ml, n_spans, span_
     second kernel does."""
     lib = library(head_dim)
     _check_slopes(slopes_log2, n_q_heads)
+    if options:
+        options.check(n_q_heads)
+        if window:
+            raise KernelError("attention: score options go without a window")
+        _check(lib, lib.qil_attn_decode_modified(
+            _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
+            c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
+            c_int(page_size), c_int(pages.shape[0]), c_float(scale), _p(slopes_log2), *options.arguments(), _stream()),
+            "attention (single tokens)", kernels=1 if tickets is not None else 2)
+        return
     _check(lib, lib.qil_attn_decode_biased(
         _p(q), _p(pages), _p(out), _p(decode_info), c_int(n_decode), _p(part_o), _p(part_ml), _p(tickets), c_int(n_spans),
         c_int(span_len), _p(block_table), c_int(block_table.shape[1]), c_int(n_q_heads), c_int(n_kv_heads),
@@ -265,9 +308,9 @@ def attend_projection(ctx, qkv, cache, out, n_q_heads, n_kv_heads, own_kv_heads,
         "attention (single tokens from the projection)", kernels=1 if tickets is not None else 2)
 
 
-def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, slopes_log2=None):
+def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, slopes_log2=None, options=None):
     """q, out bfloat16 [N, Hq*D]; cache a KVCacheView whose pages already hold this step's keys and values.
-    ``slopes_log2``: see ``prefill``."""
+    ``slopes_log2``, ``options``: see ``prefill``."""
     if q.dtype != torch.bfloat16 or cache.pages.dtype != torch.bfloat16:
         raise KernelError("the tensor-core attention takes bfloat16 queries and pages")
     if tuple(cache.pages.shape[1:]) != (2, n_kv_heads, cache.page_size, head_dim):
@@ -275,7 +318,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
     arrays, counts = step_plan(ctx)
     n_tiles, n_big, n_rest, n_decode = (counts[name] // 4 for name in
                                         ("tile_info", "big_tile_info", "rest_tile_info", "decode_info"))
-    if n_big and attention_tc.supports(head_dim, cache.page_size, window):
+    if n_big and not options and attention_tc.supports(head_dim, cache.page_size, window):
         # whole 128-token tiles on tcgen05 with the accumulators in tensor memory, the leftovers below
         attention_tc.prefill(q, cache.pages, out, arrays["big_tile_info"], n_big, cache.block_table,
                              n_q_heads, n_kv_heads, cache.page_size, scale, slopes_log2=slopes_log2)
@@ -284,7 +327,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
                     n_kv_heads, head_dim, cache.page_size, window, scale, slopes_log2)
     elif n_tiles:
         prefill(q, cache.pages, out, arrays["tile_info"], n_tiles, cache.block_table, n_q_heads, n_kv_heads,
-                head_dim, cache.page_size, window, scale, slopes_log2)
+                head_dim, cache.page_size, window, scale, slopes_log2, options)
     if n_decode:
         n_spans, longest_span = plan_spans(n_decode, n_q_heads, n_kv_heads, ctx.max_context, head_dim,
                                            getattr(ctx, "min_context", 0) or None)
@@ -292,4 +335,5 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
         if not merge_in_kernel(n_decode, n_q_heads, n_kv_heads, head_dim):
             tickets = None
         decode(q, cache.pages, out, arrays["decode_info"], n_decode, part_o, part_ml, n_spans, -longest_span,
-               cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets, slopes_log2)
+               cache.block_table, n_q_heads, n_kv_heads, head_dim, cache.page_size, window, scale, tickets, slopes_log2,
+               options)

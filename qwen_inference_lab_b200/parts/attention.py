@@ -130,7 +130,7 @@ class GroupedQueryAttention(Mixer):
             distance_rows(self.distance_bias[0], self.distance_bias[1], 1)      # refuses constants that do not fit
             self.distance_table = Param((self.distance_bias[0], self.n_q_heads), std=0.5)
             self._extra[names["distance_bias"]] = self.distance_table
-        self._conv_w = self._bias_by_distance = None
+        self._conv_w = self._bias_by_distance = self._options = None
         self.q_norm = self.k_norm = None
         self._norm_names = None
         if qk_norm_eps is not None:
@@ -170,6 +170,7 @@ class GroupedQueryAttention(Mixer):
                 count = max(1, min(count, self.chunk))
             index = torch.tensor(of_distance[:count], dtype=torch.long, device=self.distance_table.data.device)
             self._bias_by_distance = self.distance_table.data.float()[index].t().contiguous()
+        self._options = attention_mma.ScoreOptions(self.softcap, self._bias_by_distance, self.chunk, self.sink)
 
     def step_planners(self):
         return {**super().step_planners(), _PLANNER.key: _PLANNER}
@@ -253,6 +254,12 @@ class GroupedQueryAttention(Mixer):
         return self.out.forward(ctx, attended, residual=residual)
 
     def _attend(self, ctx, q, cache, out):
+        tensor_cores = q.dtype == torch.bfloat16 and self.v_head_dim == self.head_dim \
+            and attention_mma.supports(self.head_dim, self.n_q_heads, self.n_kv_heads)
+        if self.modified_scores and tensor_cores:
+            attention_mma.attend(ctx, q, cache, out, self.n_q_heads, self.n_kv_heads, self.head_dim, 0, self.scale,
+                                 self._slopes_log2, self._options)
+            return
         if self.modified_scores:
             ops.attention_generic(q, cache.pages, out, ctx.positions, ctx.token_row, cache.block_table,
                                   self.n_q_heads, self.n_kv_heads, self.head_dim, cache.page_size,

@@ -262,6 +262,111 @@ def test_the_distance_table_and_the_sink_alone(dtype):
     assert float(plain.sink_softmax(bias[0, distance].double()).sum()) < 1.0
 
 
+def paged_pool(keys, values, page, seed):
+    """keys, values: lists of [T, G, d] per request -> (pages [P, 2, G, page, d] bfloat16 with NaN where nothing was
+    written, block table int32 [requests, width]); page ids are shuffled."""
+    G, d = keys[0].shape[1:]
+    counts = [(k.shape[0] + page - 1) // page for k in keys]
+    total = sum(counts) + 3
+    order = torch.randperm(total, generator=torch.Generator().manual_seed(seed)).tolist()
+    pages = torch.full((total, 2, G, page, d), float("nan"), dtype=torch.bfloat16)
+    table = torch.full((len(keys), max(counts) + 1), -1, dtype=torch.int32)
+    for r, (k, v) in enumerate(zip(keys, values)):
+        for i in range(counts[r]):
+            pid = order.pop()
+            table[r, i] = pid
+            n = min(page, k.shape[0] - i * page)
+            pages[pid, 0, :, :n] = k[i * page:i * page + n].transpose(0, 1).to(torch.bfloat16)
+            pages[pid, 1, :, :n] = v[i * page:i * page + n].transpose(0, 1).to(torch.bfloat16)
+    return pages, table
+
+
+def run_tensor_core_attention(q_rows, positions, request, pages, table, heads, kv_heads, d, page, scale, options, span_len=None,
+                              tickets=False):
+    """Consecutive positions of one request through the tiled kernel (``span_len`` None) or, every row a single
+    token of its own, through the span kernel (its merge kernel, or the ticket form)."""
+    from qwen_inference_lab_b200.kernels import attention_mma
+    n = q_rows.shape[0]
+    as_int = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    out = torch.full((n, heads * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    q = q_rows.reshape(n, heads * d).to(torch.bfloat16).cuda()
+    if span_len is None:
+        info = [v for first in range(0, n, 64) for v in (first, positions[first], min(64, n - first), request)]
+        attention_mma.prefill(q, pages.cuda(), out, as_int(info), len(info) // 4, table.cuda(), heads, kv_heads, d, page, 0,
+                              scale, None, options)
+        return out
+    longest = max(positions) + 1
+    n_spans = (longest + span_len - 1) // span_len
+    info = [v for i in range(n) for v in (i, positions[i], request, longest)]
+    part_o = torch.full((n * heads * n_spans * d,), float("nan"), device="cuda")
+    part_ml = torch.full((n * heads * n_spans * 2,), float("nan"), device="cuda")
+    counters = torch.zeros(n * heads, dtype=torch.int32, device="cuda") if tickets else None
+    attention_mma.decode(q, pages.cuda(), out, as_int(info), n, part_o, part_ml, n_spans, span_len, table.cuda(), heads,
+                         kv_heads, d, page, 0, scale, counters, None, options)
+    return out
+
+
+@pytest.mark.parametrize("heads,kv_heads,d,chunk,cap,rows_,farthest,page", [
+    (4, 2, 96, 200, 20.0, 32, 240, 16), (6, 2, 32, 48, 15.0, 16, 100, 4), (2, 1, 80, 128, 50.0, 32, 500, 16),
+    (3, 3, 16, 7, 8.0, 10, 30, 8), (8, 2, 64, 33, 10.0, 10, 40, 16), (20, 1, 48, 150, 0.0, 8, 64, 8)])
+def test_tensor_core_attention_with_score_options(heads, kv_heads, d, chunk, cap, rows_, farthest, page):
+    """The tiled kernel and the span kernel (short and long spans, merged by a second kernel and by tickets: the same
+    bits) with cap, distance table, chunks and sink, on shuffled pages beside another request's, against the plain
+    attention; the prompt's tiles and the single tokens straddle chunk edges."""
+    from qwen_inference_lab_b200.kernels import attention_mma
+    from qwen_inference_lab_b200.parts.attention import distance_rows
+    T = 331
+    generator = torch.Generator().manual_seed(d + chunk)
+    q = (torch.randn(T, heads, d, generator=generator) * 1.5).to(torch.bfloat16).float()
+    k = (torch.randn(T, kv_heads, d, generator=generator) * 1.5).to(torch.bfloat16).float()
+    v = torch.randn(T, kv_heads, d, generator=generator).to(torch.bfloat16).float()
+    other = torch.randn(70, kv_heads, d, generator=generator)
+    pages, table = paged_pool([other, k], [other, v], page, seed=chunk)
+    learned = torch.randn(rows_, heads, generator=generator).to(torch.bfloat16).float()
+    scale = d ** -0.5
+    m = dict(scale=scale, softcap=cap, bias_max=farthest, mask=dict(size=chunk))
+    expected = plain.chunk_attention(q.double(), k.double(), v.double(), m, learned.double()).reshape(T, heads * d)
+    by_distance = learned[torch.tensor(distance_rows(rows_, farthest, farthest + 1))].t().contiguous().cuda()
+    options = attention_mma.ScoreOptions(cap, by_distance, chunk, True)
+    out = run_tensor_core_attention(q, list(range(T)), 1, pages, table, heads, kv_heads, d, page, scale, options)
+    close(out, expected, torch.bfloat16)
+    late = run_tensor_core_attention(q[150:], list(range(150, T)), 1, pages, table, heads, kv_heads, d, page, scale, options)
+    close(late, expected[150:], torch.bfloat16)
+    singles = sorted({0, 1, chunk - 1, chunk, chunk + 1, 2 * chunk - 1, 2 * chunk, 63, 64, 65, 127, 128, 255, 256, 300, T - 1} & set(range(T)))
+    for span_len in (64, 128, 2048):
+        merged = run_tensor_core_attention(q[singles], singles, 1, pages, table, heads, kv_heads, d, page, scale, options, span_len)
+        close(merged, expected[singles], torch.bfloat16)
+        by_tickets = run_tensor_core_attention(q[singles], singles, 1, pages, table, heads, kv_heads, d, page, scale, options,
+                                               span_len, tickets=True)
+        assert torch.equal(merged, by_tickets)
+
+
+@pytest.mark.parametrize("single", [False, True], ids=["prompt", "decoded"])
+@pytest.mark.parametrize("chunk,query,far", [(64, 127, 64), (64, 128, 127), (64, 128, 64), (200, 399, 200), (200, 400, 399),
+                                             (7, 13, 7), (7, 14, 13), (128, 127, 0), (128, 128, 0), (33, 65, 33), (33, 66, 65)])
+def test_a_key_at_the_chunks_edge_through_the_tensor_core_kernels(single, chunk, query, far):
+    """The standing-out key of the test above through the tiled kernel (the query is the last row of a five-token
+    portion) and the span kernel: seen from inside its chunk, not from the first position of the next."""
+    from qwen_inference_lab_b200.kernels import attention_mma
+    heads, kv_heads, d, page, cap = 2, 1, 32, 8, 20.0
+    n_tokens = 1 if single else 5
+    first = query - n_tokens + 1
+    q, k, _, T = _scores_case(torch.bfloat16, n_tokens, first, far, chunk)
+    v = rows(T, kv_heads * d, 41).view(T, kv_heads, d)
+    pages, table = paged_pool([k], [v], page, seed=query)
+    options = attention_mma.ScoreOptions(cap, torch.zeros(heads, 4, device="cuda"), chunk, True)
+    positions = list(range(first, query + 1))
+    out = run_tensor_core_attention(q, positions, 0, pages, table, heads, kv_heads, d, page, 1.0, options,
+                                    span_len=64 if single else None, tickets=single)
+    got = out[-1].view(heads, d).float().cpu()
+    if far // chunk == query // chunk:
+        close(got, v[far].expand(heads, d), torch.bfloat16)
+    else:
+        assert (got - v[far]).abs().max() > 0.05
+        own = v[query // chunk * chunk:query + 1, 0].double()
+        close(got, (own.sum(0) / (own.shape[0] + 1)).expand(heads, d), torch.bfloat16)      # equal weights, and the sink's
+
+
 def experts_part(dtype, experts, identity, top, shared, hidden=40, ff=24, scale=1.7, seed=3):
     from qwen_inference_lab_b200.parts import PlainMLP, RoutedExperts
     shared_part = PlainMLP(hidden, shared, names=dict(up="f.shared.up", down="f.shared.down"), suffixes=("", ".b")) if shared else None
