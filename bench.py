@@ -627,6 +627,207 @@ def run_virulix(args):
         torch.cuda.empty_cache()
 
 
+# --------------------------------------------------------------------------- Debisun beside Virulix
+def _debisun_sizes(width, heads, kv_heads, dim, dense_ff, experts, identity, top, expert_ff, shared_ff, side, chunk, vocab):
+    """Eight layers that use every mechanism of the design at one width."""
+    mixer = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, conv=4, softcap=30.0, bias_max=1024,
+                 bias_rows=32, mask=dict(size=chunk))
+    moe = dict(kind="moe", router=dict(experts=experts, identity=identity, top=top, scale=2.5), expert=dict(ff=expert_ff),
+               shared=dict(ff=shared_ff))
+    dense = dict(kind="dense", ff=dense_ff)
+    layers = [dict(type="attention", mixer=mixer, mlp=mlp) for mlp in (dense, moe, moe, moe, moe, dense, dense, moe)]
+    return dict(architecture="Debisun", vocab=vocab, width=width, norm=dict(eps=1e-6), token_side=dict(dim=side), layers=layers)
+
+
+def _virulix_like(width, heads, kv_heads, dim, dense_ff, experts, top, expert_ff, shared_ff, vocab, **_):
+    """Virulix with attention in every layer and the same order of dense and routed feed-forwards."""
+    mixer = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, q_temp=dict(coef=0.1, every=256))
+    moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff, limit=7.0),
+               shared=dict(ff=shared_ff, limit=7.0))
+    dense = dict(kind="dense", ff=dense_ff)
+    layers = [dict(type="attention", mixer=mixer, mlp=mlp) for mlp in (dense, moe, moe, moe, moe, dense, dense, moe)]
+    return dict(architecture="Virulix", vocab=vocab, width=width, norm=dict(eps=1e-6), layers=layers)
+
+
+DEBISUN_SHAPES = {
+    "2048": dict(width=2048, heads=16, kv_heads=4, dim=128, dense_ff=6144, experts=32, identity=4, top=4, expert_ff=768,
+                 shared_ff=1536, side=64, chunk=1024, vocab=32768),
+    "4096": dict(width=4096, heads=32, kv_heads=8, dim=128, dense_ff=12288, experts=64, identity=8, top=6, expert_ff=1024,
+                 shared_ff=2048, side=128, chunk=1024, vocab=32768),
+}
+
+
+def _debisun_kernels(torch, debisun, virulix, sizes, pk, tokens_n, batch, context, flush):
+    """The kernels of Debisun's mechanisms alone, each beside the like kernel of Virulix, with what the roofline
+    allows: (name, ms, fraction of the measured peak, of what)."""
+    from qwen_inference_lab_b200.cache import CacheManager
+    from qwen_inference_lab_b200.engine import StepEntry, StepRunner
+    from qwen_inference_lab_b200.kernels import ops
+    from tests.harness import OnePartModel
+    rows = []
+    H, G, d, W = sizes["heads"], sizes["kv_heads"], sizes["dim"], sizes["width"]
+    tflops, gbs = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+
+    class Timer:
+        def __init__(self):
+            self.ms = []
+        def __call__(self, fn):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            out = fn()
+            stop.record()
+            self.ms.append((start, stop))
+            return out
+        def median(self, skip):
+            torch.cuda.synchronize()
+            values = [a.elapsed_time(b) for a, b in self.ms[skip:]]
+            self.ms = []
+            return statistics.median(values)
+
+    def measure(name, part, hidden, kernel_of, prompt_work, decode_bytes, stream_dtype=None):
+        """``prompt_work``: (FLOPs, None) for a kernel bound by arithmetic, (None, bytes) for one bound by memory."""
+        timer = Timer()
+        shell = OnePartModel(part, hidden, torch.bfloat16, lambda ctx, x, view: kernel_of(ctx, x, view, timer))
+        shell.stream_dtype = stream_dtype
+        shell.inputs = torch.randn(4096, hidden, device="cuda").to(torch.bfloat16)
+        pages = (batch + 1) * ((max(tokens_n, context) + PAGE_SIZE) // PAGE_SIZE + 2)
+        cache = CacheManager(shell.cache_specs(), num_pages=pages, page_size=PAGE_SIZE, max_requests=batch + 1,
+                             max_context=pages * PAGE_SIZE, dtype=torch.bfloat16, device="cuda")
+        for g in cache.kv_groups:
+            g.storage.normal_(0.0, 0.5)
+        runner = StepRunner(shell, cache, max_step_tokens=tokens_n, use_graphs=False)
+        ids = [i % 4096 for i in range(tokens_n)]
+        for i in range(8):
+            flush.zero_()
+            cache.admit("p")
+            runner.run([StepEntry("p", ids, [])])
+            cache.release("p")
+            shell.outputs.clear()
+        ms = timer.median(3)
+        flops, moved = prompt_work
+        if flops is not None:
+            rows.append((f"{name} prompt {tokens_n}", ms, flops / (ms * 1e-3) / tflops, "of the bf16 peak"))
+        else:
+            rows.append((f"{name} prompt {tokens_n}", ms, moved / (ms * 1e-3) / gbs, "of the copy bandwidth"))
+        for rid in range(batch):
+            cache.admit(rid)
+            cache.ensure(rid, context)
+            cache.advance(rid, context)
+        for i in range(12):
+            flush.zero_()
+            runner.run([StepEntry(rid, [rid], []) for rid in range(batch)])
+            shell.outputs.clear()
+        ms = timer.median(4)
+        rows.append((f"{name} decode b{batch} c{context}", ms, decode_bytes / (ms * 1e-3) / gbs, "of the copy bandwidth"))
+
+    def attention_kernel(mixer):
+        def kernel(ctx, x, view, timer):
+            q = x[:, :H * d].contiguous()
+            out = torch.empty_like(q)
+            view = view[0] if isinstance(view, tuple) else view
+            timer(lambda: mixer._attend(ctx, q, view, out))
+            return out
+        return kernel
+
+    ours, theirs = debisun.layers[0].mixer, virulix.layers[0].mixer
+    chunk = ours.chunk
+    seen = lambda n: sum(min(i % chunk, i) + 1 for i in range(n)) if chunk else n * (n + 1) // 2      # (query, key) pairs
+    decode_keys = lambda c: (c % chunk + 1) if chunk else c + 1
+    measure("debisun attention (cap, distance table, chunks, sink)", ours, H * d, attention_kernel(ours),
+            (4.0 * H * d * seen(tokens_n), None), batch * decode_keys(context) * 2 * G * d * 2)
+    measure("virulix attention (distance slopes)", theirs, H * d, attention_kernel(theirs),
+            (4.0 * H * d * tokens_n * (tokens_n + 1) / 2, None), batch * (context + 1) * 2 * G * d * 2)
+
+    channels = (H + 2 * G) * d
+    def conv_kernel(ctx, x, view, timer):
+        qkv = x[:, :channels].contiguous()
+        q = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
+        pages_view, state = view
+        timer(lambda: ops.short_conv_store(qkv, ours._conv_w, state.slots, q, pages_view.pages, ctx.positions, ctx.token_row,
+                                           pages_view.block_table, ctx.seg_row, ctx.seg_start, ctx.seg_len, ctx.n_segments,
+                                           H, G, d, d, pages_view.page_size))
+        return q
+    def store_kernel(ctx, x, view, timer):
+        qkv = x[:, :channels].contiguous()
+        q = torch.empty((x.shape[0], H * d), dtype=x.dtype, device=x.device)
+        timer(lambda: ops.qkv_store(qkv, q, view.pages, ctx.positions, ctx.token_row, view.block_table, H, G, d, d,
+                                    view.page_size, 0.1, 256))
+        return q
+    moved = lambda n: 2 * n * channels * 2          # every row read once and written once
+    measure("debisun short convolution + page write", ours, channels, conv_kernel, (None, moved(tokens_n)), moved(batch))
+    measure("virulix query temperature + page write", theirs, channels, store_kernel, (None, moved(tokens_n)), moved(batch))
+
+    moe = next(l.feed_forward for l in debisun.layers if hasattr(l.feed_forward, "n_experts"))
+    ff, E, top = moe.expert_size, moe.n_experts, moe.top
+    def moe_kernel(ctx, x, view, timer):
+        h = x[:, :W].contiguous()
+        chosen, weights = ops.moe_route(h, moe.router.data, None, top, softmax_all=True, correction=moe.correction.data,
+                                        weight_scale=moe.weight_scale)
+        return timer(lambda: ops.moe_experts(h, chosen, weights, moe._up, None, moe._down, moe.activation, identity=True))
+    measure("debisun routed experts (no gate matrix, identity outputs)", moe, W, moe_kernel,
+            (2.0 * tokens_n * top * 2 * ff * W * E / (E + moe.identity), None), min(E, batch * top) * 2 * ff * W * 2)
+    other = next(l.feed_forward for l in virulix.layers if hasattr(l.feed_forward, "n_experts"))
+    def other_kernel(ctx, x, view, timer):
+        h = x[:, :W].contiguous()
+        chosen, weights = ops.moe_route(h, other.router.data, other.router_bias.data, other.top)
+        return timer(lambda: ops.moe_experts(h, chosen, weights, other._gate, other._up, other._down, other.activation,
+                                             limit=other.limit, alpha=other.alpha))
+    measure("virulix routed experts (gated)", other, W, other_kernel, (2.0 * tokens_n * other.top * 3 * other.expert_size * W, None),
+            min(other.n_experts, batch * other.top) * 3 * other.expert_size * W * 2)
+
+    def ff_kernel(part):
+        def kernel(ctx, x, view, timer):
+            h = x[:, :W].contiguous()
+            return timer(lambda: part.forward(ctx, h))
+        return kernel
+    dense = next(l.feed_forward for l in debisun.layers if hasattr(l.feed_forward, "up") and not hasattr(l.feed_forward, "n_experts"))
+    inner = dense.intermediate_size
+    measure("debisun feed-forward (squared relu)", dense, W, ff_kernel(dense), (2.0 * tokens_n * 2 * inner * W, None), 2 * inner * W * 2)
+    gated = next(l.feed_forward for l in virulix.layers if hasattr(l.feed_forward, "gate_up"))
+    measure("virulix feed-forward (gated gelu)", gated, W, ff_kernel(gated), (2.0 * tokens_n * 3 * inner * W, None), 3 * inner * W * 2)
+
+    side = debisun.layers[0].after[0]
+    def side_kernel(ctx, x, view, timer):
+        stream = x[:, :W].float()
+        return timer(lambda: side.forward(ctx, stream))
+    # the stream is read and written in float32 and read once more in bfloat16; the two matrices are small
+    side_bytes = lambda n: n * W * (4 + 4 + 4 + 2 + 2) + 2 * side.dim * W * 2
+    measure("debisun token side input (5 kernels)", side, W, side_kernel, (None, side_bytes(tokens_n)), side_bytes(batch))
+    return rows
+
+
+def run_debisun(args):
+    """Prefill and decode of Debisun at sizes like a real model's layers, beside Virulix (the engine's closest
+    design: float32 stream, attention with a distance bias, routed experts with a shared one) of equal width, heads,
+    layer count, feed-forward sizes and vocabulary, and the kernels of its mechanisms against their rooflines."""
+    import torch
+    from qwen_inference_lab_b200.config.model_config import DebisunConfig, VirulixConfig
+    from qwen_inference_lab_b200.loading import random_model
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in ([args.debisun_shape] if args.debisun_shape else sorted(DEBISUN_SHAPES)):
+        sizes = DEBISUN_SHAPES[name]
+        debisun = random_model(DebisunConfig.from_dict(_debisun_sizes(**sizes)), seed=0, device="cuda", dtype=torch.bfloat16)
+        virulix = random_model(VirulixConfig.from_dict(_virulix_like(**sizes)), seed=0, device="cuda", dtype=torch.bfloat16)
+        result = {"workload": "debisun", "width": sizes["width"], "layers": 8, "dtype": "bfloat16",
+                  "peaks": "of measured" if pk["source"] == "measured" else "of fallback", "models": {}, "kernels": []}
+        for label, model in (("debisun", debisun), ("virulix", virulix)):
+            bench = _ModelBench(model, sizes["vocab"])
+            entry = {}
+            for tokens_n in (512, 2048):
+                ms = bench.prefill(tokens_n, flush)
+                entry[f"prefill_{tokens_n}"] = {"ms": round(ms, 3), "tokens_per_s": round(tokens_n / ms * 1e3, 1)}
+            for batch, context in ((1, 2048), (8, 2048), (32, 2048)):
+                ms = bench.decode(batch, context, args.steps, max(args.warmup, 6))
+                entry[f"decode_b{batch}_c{context}"] = {"ms": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1)}
+            result["models"][label] = entry
+        for kernel, ms, frac, of in _debisun_kernels(torch, debisun, virulix, sizes, pk, 2048, 8, 2048 + 511, flush):
+            result["kernels"].append({"kernel": kernel, "ms": round(ms, 4), "frac": round(frac, 4), "of": of})
+        print(json.dumps(result), flush=True)
+        del debisun, virulix
+        torch.cuda.empty_cache()
+
+
 # --------------------------------------------------------------------------- the reference
 def run_reference(args):
     ref = ROOT / "baseline" / "_ref"
@@ -714,12 +915,15 @@ def main():
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     parser.add_argument("--quick", action="store_true", help="skip the batch 1 and 64 points")
-    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "virulix"], default=None,
+    parser.add_argument("--only", choices=["decode", "prefill", "mixed", "virulix", "debisun"], default=None,
                         help="run just this part and print its result instead of the JSON line; mixed = 64 requests "
                              "with prompts of 16 to 2048 tokens and 128 new tokens each through Engine.generate; "
-                             "virulix = the Virulix design beside dense Qwen3 of equal size, and its mixers' kernels")
+                             "virulix = the Virulix design beside dense Qwen3 of equal size, and its mixers' kernels; "
+                             "debisun = the Debisun design beside Virulix of equal size, and its mechanisms' kernels")
     parser.add_argument("--virulix-shape", choices=sorted(VIRULIX_SHAPES), default=None,
                         help="width of --only virulix (default: all)")
+    parser.add_argument("--debisun-shape", choices=sorted(DEBISUN_SHAPES), default=None,
+                        help="width of --only debisun (default: all)")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes (default: Qwen3-8B)")
     parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     parser.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request (profiling aid)")
@@ -733,6 +937,9 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.only == "debisun":
+        run_debisun(args)
+        return 0
     if args.only == "virulix":
         run_virulix(args)
         return 0

@@ -98,27 +98,32 @@ struct AttnParams {
     const float* slopes_log2;
     // Options that the MOD forms of the kernels apply (all float32, the score in natural units until the end):
     //   softcap > 0   score <- softcap * tanh(q.k * scale / softcap), before any bias
-    //   dist_bias     float32 [Hq][dist_len]: added by distance (query position - key position), the last entry for
-    //                 every distance beyond the table
+    //   dist_bias     float32 [Hq][dist_len], the learned values times log2(e): added by distance (query position -
+    //                 key position), the last entry for every distance beyond the table
     //   chunk > 0     a query sees only the keys of its own chunk of that many positions (counted from position 0)
     //   sink          one is added to the softmax's denominator (a key of score 0 without a value)
     float scale, softcap;
-    const float* dist_bias;
+    float tanh_arg, cap_log2;   // 2 log2(e) scale / softcap and softcap log2(e): see modified_score_log2
+    const float* dist_bias;     // times log2(e)
     int dist_len, chunk, sink;
 };
 
-// tanh from one exponential: absolute error of a few 1e-7, which the cap multiplies.
-__device__ __forceinline__ float tanh_from_exp(float x) {
-    return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f);
-}
-
-// The modified score in units of log2: cap, distance table, slope.  `bias_row` is the query head's row of the table.
+// The modified score in units of log2: cap, distance table, slope.  tanh comes from one exponential,
+// tanh(x) = 1 - 2 / (e^(2x) + 1), with the constants folded on the host: absolute error of a few 1e-7 times the cap.
+// `bias_row` is the query head's row of the table (already times log2(e)).
 __device__ __forceinline__ float modified_score_log2(const AttnParams& p, float dot, int distance, float slope_log2,
                                                      const float* __restrict__ bias_row) {
-    float score = dot * p.scale;
-    if (p.softcap > 0.f) score = p.softcap * tanh_from_exp(score / p.softcap);
-    if (bias_row != nullptr) score += __ldg(bias_row + min(distance, p.dist_len - 1));
-    return fmaf(-(float)distance, slope_log2, score * 1.4426950408889634f);
+    float v;
+    if (p.softcap > 0.f) {
+        float r;
+        asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(fast_exp2(dot * p.tanh_arg) + 1.f));
+        v = fmaf(-2.f * p.cap_log2, r, p.cap_log2);
+    } else {
+        v = dot * p.scale_log2;
+    }
+    if (bias_row != nullptr) v += __ldg(bias_row + min(distance, p.dist_len - 1));
+    if (slope_log2 != 0.f) v = fmaf(-(float)distance, slope_log2, v);
+    return v;
 }
 
 // Where the key row of position ``pos`` of one kv head starts, in units of 16 bytes from the layer's
@@ -255,13 +260,15 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
         float tmax_a = -INFINITY, tmax_b = -INFINITY;
         const bool full = !MOD && (tile + 1) * KV_TILE - 1 <= pos0 && (p.window == 0 || tile * KV_TILE > hi - p.window);
         if (MOD) {
+            // a tile that lies at or before the first row's position and inside the last row's chunk needs no mask
+            const bool inside = (tile + 1) * KV_TILE - 1 <= pos0 && (p.chunk == 0 || tile * KV_TILE >= hi / p.chunk * p.chunk);
 #pragma unroll
             for (int nt = 0; nt < KV_TILE / 8; ++nt) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int key = tile * KV_TILE + nt * 8 + (lane & 3) * 2 + (e & 1);
                     const int pos = (e < 2) ? pos_a : pos_b;
-                    const bool ok = key <= pos && key >= ((e < 2) ? lo_a : lo_b) && (p.window == 0 || key > pos - p.window);
+                    const bool ok = inside || (key <= pos && key >= ((e < 2) ? lo_a : lo_b));
                     const float v = ok ? modified_score_log2(p, s[nt][e], pos - key, slope, bias_row) : -INFINITY;
                     s[nt][e] = v;
                     if (e < 2) tmax_a = fmaxf(tmax_a, v); else tmax_b = fmaxf(tmax_b, v);
@@ -856,7 +863,7 @@ static int fill_params(AttnParams& p, const void* q, const void* kv, void* out, 
     p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.slopes_log2 = nullptr;
-    p.scale = scale; p.softcap = 0.f; p.dist_bias = nullptr; p.dist_len = 0; p.chunk = 0; p.sink = 0;
+    p.scale = scale; p.softcap = 0.f; p.tanh_arg = p.cap_log2 = 0.f; p.dist_bias = nullptr; p.dist_len = 0; p.chunk = 0; p.sink = 0;
     return 0;
 }
 
@@ -867,6 +874,10 @@ static int fill_options(AttnParams& p, float softcap, const float* dist_bias, in
     if ((softcap > 0.f || dist_bias != nullptr || chunk > 0 || sink) && p.window > 0)
         QIL_REFUSE("attention: a window does not go with chunks, a softcap, a distance table or a sink");
     p.softcap = softcap; p.dist_bias = dist_bias; p.dist_len = dist_len; p.chunk = chunk; p.sink = sink ? 1 : 0;
+    if (softcap > 0.f) {
+        p.tanh_arg = (float)(2.0 * 1.4426950408889634 * (double)p.scale / (double)softcap);
+        p.cap_log2 = (float)((double)softcap * 1.4426950408889634);
+    }
     return 0;
 }
 static bool has_options(const AttnParams& p) {

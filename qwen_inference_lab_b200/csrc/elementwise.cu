@@ -244,20 +244,60 @@ extern "C" int qil_add_inplace(void* x, const void* y, long long total, int act_
 // float32 arithmetic; x and y may differ in type (a float32 stream, bfloat16 branch).
 template <typename TX, typename TY>
 __global__ void __launch_bounds__(256)
-scaled_add_kernel(TX* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ scale, size_t total, int width) {
+scaled_add_kernel(TX* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ scale, int n_rows, int width) {
     qil_wait_for_producer();
     qil_release_consumer();
-    for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (size_t)gridDim.x * 256)
-        x[i] = from_f32<TX>(fmaf(scale[i % width], to_f32<TY>(y[i]), to_f32<TX>(x[i])));
+    // a block walks rows, a thread the same columns of each: no division per element, the scale read once
+    for (int col = threadIdx.x; col < width; col += 256) {
+        const float s = scale[col];
+        for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+            const size_t i = (size_t)row * width + col;
+            x[i] = from_f32<TX>(fmaf(s, to_f32<TY>(y[i]), to_f32<TX>(x[i])));
+        }
+    }
+}
+
+// float32 stream, widths that are multiples of 4: 16 bytes a load
+template <typename TY>
+__global__ void __launch_bounds__(256)
+scaled_add_f32x4_kernel(float* __restrict__ x, const TY* __restrict__ y, const float* __restrict__ scale, int n_rows, int width) {
+    qil_wait_for_producer();
+    qil_release_consumer();
+    for (int col = threadIdx.x * 4; col < width; col += 1024) {
+        const float4 s = *reinterpret_cast<const float4*>(scale + col);
+        for (int row = blockIdx.x; row < n_rows; row += gridDim.x) {
+            const size_t i = (size_t)row * width + col;
+            float4 v = *reinterpret_cast<float4*>(x + i);
+            float b[4];
+            if (sizeof(TY) == 4) {
+                const float4 t = *reinterpret_cast<const float4*>(y + i);
+                b[0] = t.x; b[1] = t.y; b[2] = t.z; b[3] = t.w;
+            } else {
+                const uint2 raw = *reinterpret_cast<const uint2*>(y + i);
+                const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                b[0] = lo.x; b[1] = lo.y; b[2] = hi.x; b[3] = hi.y;
+            }
+            v.x = fmaf(s.x, b[0], v.x); v.y = fmaf(s.y, b[1], v.y); v.z = fmaf(s.z, b[2], v.z); v.w = fmaf(s.w, b[3], v.w);
+            *reinterpret_cast<float4*>(x + i) = v;
+        }
+    }
 }
 
 extern "C" int qil_scaled_add(void* x, int x_dtype, const void* y, int y_dtype, const float* scale, int n_rows,
                               int width, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width <= 0) QIL_REFUSE("scaled_add: width %d", width);
-    const size_t total = (size_t)n_rows * width;
-    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-#define QIL_GO(TX, TY) qil_launch_chained(scaled_add_kernel<TX, TY>, dim3(blocks), dim3(256), 0, stream, (TX*)x, (const TY*)y, scale, total, width)
+    const int blocks = n_rows < 148 * 8 ? n_rows : 148 * 8;
+    if (x_dtype == QIL_F32 && width % 4 == 0 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale) & 15) == 0) {
+        if (y_dtype == QIL_F32)
+            qil_launch_chained(scaled_add_f32x4_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)y, scale, n_rows, width);
+        else if (y_dtype == QIL_BF16)
+            qil_launch_chained(scaled_add_f32x4_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const bf16*)y, scale, n_rows, width);
+        else QIL_REFUSE("scaled_add: dtypes %d += %d", x_dtype, y_dtype);
+        QIL_CHECK_LAUNCH();
+    }
+#define QIL_GO(TX, TY) qil_launch_chained(scaled_add_kernel<TX, TY>, dim3(blocks), dim3(256), 0, stream, (TX*)x, (const TY*)y, scale, n_rows, width)
     if (x_dtype == QIL_F32 && y_dtype == QIL_F32) QIL_GO(float, float);
     else if (x_dtype == QIL_F32 && y_dtype == QIL_BF16) QIL_GO(float, bf16);
     else if (x_dtype == QIL_BF16 && y_dtype == QIL_BF16) QIL_GO(bf16, bf16);

@@ -201,6 +201,8 @@ class ScoreOptions:
 
     def __init__(self, softcap=0.0, distance_bias=None, chunk=0, sink=False):
         self.softcap, self.distance_bias, self.chunk, self.sink = float(softcap or 0.0), distance_bias, int(chunk or 0), bool(sink)
+        # the kernels work in units of log2: the table times log2(e), made once
+        self._bias_log2 = None if distance_bias is None else (distance_bias.double() * 1.4426950408889634).float().contiguous()
 
     def __bool__(self):
         return bool(self.softcap or self.distance_bias is not None or self.chunk or self.sink)
@@ -212,7 +214,7 @@ class ScoreOptions:
             raise KernelError("attention: the distance table must be float32 [query heads, distances] on the device")
 
     def arguments(self):
-        bias = self.distance_bias
+        bias = self._bias_log2
         return (c_float(self.softcap), _p(bias), c_int(bias.shape[1] if bias is not None else 0), c_int(self.chunk),
                 c_int(1 if self.sink else 0))
 

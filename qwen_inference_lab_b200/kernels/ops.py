@@ -213,7 +213,7 @@ def small_m_ok(a, weight) -> bool:
 
 
 def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=False, silu_pairs=False,
-                 norm_weight=None, norm_eps=0.0, rows_per_block=None):
+                 norm_weight=None, norm_eps=0.0, rows_per_block=None, col_scale=None):
     """out = a @ weight.T (+ bias) (+ residual) for a decode step's few rows, streaming the weight once.
 
     a bfloat16 [M <= 16, K]; weight bfloat16 [N, K].  ``out_float32`` returns float32 (the LM head).
@@ -222,6 +222,7 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
     RMSNorm(a; norm_weight, norm_eps): the product of the normed rows, with no pass of its own over them.
     ``rows_per_block``: 16 or 32 output features a block (32 wants N a multiple of 32); None leaves it to the
     measured rule in ``tuning``.  The two forms add a product's terms in different orders.
+    ``col_scale`` float32 [N]: out = (a @ weight.T + bias) * col_scale + residual.
     """
     _need(a, "a", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
     m, k = a.shape
@@ -245,6 +246,10 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
         _need(norm_weight, "norm_weight", torch.bfloat16, 1)
         if norm_weight.shape[0] != k:
             raise KernelError("gemm_small_m: the norm weight must have one value per input feature")
+    if col_scale is not None:
+        _need(col_scale, "col_scale", torch.float32, 1)
+        if col_scale.shape[0] != n or silu_pairs:
+            raise KernelError("gemm_small_m: one output scale per feature, and none with silu_pairs")
     if rows_per_block is None:
         wide = (n % 32 == 0 and n // 32 >= tuning.SMALL_M_WIDE_MIN_BLOCKS
                 and (m > 8 or n * k < tuning.SMALL_M_WIDE_MAX_ELEMENTS))
@@ -253,7 +258,7 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
     _check(lib, lib.qil_gemm_small_m(_p(a), _p(weight), _p(bias), _p(residual), _p(out), _p(norm_weight),
                                      c_float(float(norm_eps)), c_int(m), c_int(n), c_int(k),
                                      c_int(1 if out_float32 else 0), c_int(1 if silu_pairs else 0),
-                                     c_int(rows_per_block), _stream()),
+                                     c_int(rows_per_block), _p(col_scale), _stream()),
            "gemm_small_m")
     return out
 
@@ -514,14 +519,14 @@ def activation(z, kind, *, table=None, ids=None, first_col=0, out=None):
 def short_conv_store(u, taps_weight, state, q_out, kv_cache, positions, token_row, block_table, seg_row, seg_start,
                      seg_len, n_segments, n_q_heads, n_kv_heads, head_dim, v_dim, page_size):
     """A short causal convolution over time on every channel of ``u`` [N, Hq*d + Hkv*d + Hkv*e] (the stacked q/k/v
-    projection), queries to ``q_out``, keys and values into the pages.  ``taps_weight`` [channels, taps];
+    projection), queries to ``q_out``, keys and values into the pages.  ``taps_weight`` [taps, channels];
     ``state`` float32 [slots, taps - 1, channels]: the last rows of ``u`` that each request has seen, read for
     the positions before a step's first token and moved on.  Segments are the step's (int32 device arrays)."""
     _need(u, "u", ndim=2); _need(q_out, "q_out", u.dtype, 2); _need(taps_weight, "taps_weight", ndim=2)
     n, channels = u.shape
-    taps = taps_weight.shape[1]
+    taps = taps_weight.shape[0]
     if channels != n_q_heads * head_dim + n_kv_heads * (head_dim + v_dim) or q_out.shape != (n, n_q_heads * head_dim) \
-            or taps_weight.shape[0] != channels:
+            or taps_weight.shape[1] != channels:
         raise KernelError("short_conv_store: shapes do not match the head counts")
     _need(state, "state", torch.float32, 3)
     if tuple(state.shape[1:]) != (taps - 1, channels):

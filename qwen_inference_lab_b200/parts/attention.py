@@ -157,7 +157,7 @@ class GroupedQueryAttention(Mixer):
             self._slopes = torch.tensor(self.distance_slopes, dtype=torch.float32, device=device)
             self._slopes_log2 = (self._slopes.double() * 1.4426950408889634).float().contiguous()
         if self.conv is not None:
-            self._conv_w = torch.cat([p.data for p in self.conv], dim=0).contiguous()
+            self._conv_w = torch.cat([p.data for p in self.conv], dim=0).t().contiguous()     # [taps, channels]
             for p in self.conv:
                 p.data = None
         if self.distance_table is not None:

@@ -70,6 +70,10 @@ class Linear(Part):
             if residual is None or out is not None:
                 raise ValueError("an output scale goes with a residual, which is updated in place")
             if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
+                if norm is None and ops.small_m_ok(x, weight):
+                    # a decode step's few rows: scale and residual in the weight-streaming kernel's epilogue
+                    return ops.gemm_small_m(x, weight, bias=bias, residual=residual, out=residual, col_scale=out_scale,
+                                            out_float32=residual.dtype == torch.float32)
                 branch = self.forward(ctx, x, out_float32=residual.dtype == torch.float32, norm=norm)
                 return ops.scaled_add(residual, branch, out_scale)
             if norm is not None:

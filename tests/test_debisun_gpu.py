@@ -166,7 +166,7 @@ def test_short_convolution_with_state_under_every_cut(dtype, taps):
             seg_start = torch.tensor(np.cumsum([0] + [n for _, n in batch])[:-1], dtype=torch.int32, device="cuda")
             seg_row = torch.tensor([0 if rid == "a" else 1 for rid, _ in batch], dtype=torch.int32, device="cuda")
             q = torch.empty((x.shape[0], heads * d), dtype=dtype, device="cuda")
-            ops.short_conv_store(x, weight.to(dtype).cuda(), state, q, pages, positions, token_row, table, seg_row, seg_start,
+            ops.short_conv_store(x, weight.t().contiguous().to(dtype).cuda(), state, q, pages, positions, token_row, table, seg_row, seg_start,
                                  seg_len, len(batch), heads, kv_heads, d, e, page)
             at = 0
             for rid, n in batch:
