@@ -62,11 +62,11 @@ def test_configuration_round_trip_and_optional_keys():
 
 def test_distance_rows_follow_the_logarithm():
     # below half the rows a distance is its own row; from `farthest` on everything is the last row
-    rows = distance_rows(32, 240, 400)
-    assert rows[:16] == list(range(16)) and rows[16] == 16 and rows[239] == 31 and rows[240] == 31 and rows[399] == 31
+    rows = distance_rows(28, 310, 400)
+    assert rows[:14] == list(range(14)) and rows[14] == 14 and rows[309] == 27 and rows[310] == 27 and rows[399] == 27
     assert all(b >= a for a, b in zip(rows, rows[1:]))
-    for n in (17, 31, 32, 33, 100, 200, 239):
-        assert rows[n] == min(31, 16 + math.floor(math.log(n / 16) / math.log(240 / 16) * 16))
+    for n in (15, 27, 28, 29, 100, 200, 309):
+        assert rows[n] == min(27, 14 + math.floor(math.log(n / 14) / math.log(310 / 14) * 14))
     for table, farthest in ((8, 64), (10, 30), (24, 300), (16, 100)):
         ours = distance_rows(table, farthest, farthest + 5)
         assert ours == [plain.distance_bucket(n, table, farthest) for n in range(farthest + 5)]
@@ -95,7 +95,7 @@ def test_plain_functions_against_closed_forms():
 
 def test_chunk_attention_sees_its_own_chunk_only():
     """A key that would dominate is seen from inside its chunk and not from the chunk after it."""
-    m = dict(scale=1.0, softcap=20.0, bias_max=30, mask=dict(size=5))
+    m = dict(scale=1.0, softcap=18.0, bias_max=30, mask=dict(size=5))
     table = torch.zeros(8, 1, dtype=torch.float64)
     T = 12
     q = torch.zeros(T, 1, 4, dtype=torch.float64); k = torch.zeros(T, 1, 4, dtype=torch.float64)
@@ -103,7 +103,7 @@ def test_chunk_attention_sees_its_own_chunk_only():
     k[4, 0, 0] = 100.0                       # the last position of chunk 0
     q[:, 0, 0] = 100.0
     out = plain.chunk_attention(q, k, v, m, table).flatten()
-    assert abs(out[4].item() - 5.0) < 1e-6    # position 4 sees key 4 at the cap: exp(20) outweighs everything
+    assert abs(out[4].item() - 5.0) < 1e-6    # position 4 sees key 4 at the cap: exp(18) outweighs everything
     assert out[5].item() < 6.0 / 2 + 1e-9 and abs(out[5].item() - 6.0 / 2) < 1e-9     # position 5 sees itself and the sink only
     assert abs(out[9].item() - (6 + 7 + 8 + 9 + 10) / 6.0) < 1e-9
 
