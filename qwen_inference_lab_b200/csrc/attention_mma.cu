@@ -157,21 +157,18 @@ __device__ __forceinline__ void issue_kv_tile(const AttnParams& p, const int* ro
 }
 
 // ------------------------------------------------------------------ prompt portions
+// One query tile of one head: the whole of a block's work in the plain form, half of it in the MOD form.
 template <bool MOD>
-__global__ void __launch_bounds__(128, (QIL_HEAD_DIM <= 128) ? 3 : 1)
-attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+__device__ __forceinline__ void attn_prefill_tile(const AttnParams& p, const int4 info, const int head,
+                                                  unsigned char* smem_raw) {
     // [K stage 0][K stage 1][V stage 0][V stage 1]; when the queries live in registers (head sizes up to
     // 128) their tile borrows K stage 1 until the fragments are loaded, else it has a region of its own
     bf16* sK = reinterpret_cast<bf16*>(smem_raw);      // [2][64][LDS]
     bf16* sV = sK + 2 * KV_TILE * LDS;                  // [2][64][LDS]
     bf16* sQ = Q_IN_REGS ? sK + KV_TILE * LDS : sV + 2 * KV_TILE * LDS;   // [64][LDS]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // heads vary fastest, so all heads of the longest tile start first (tiles come sorted, longest first)
-    const int head = blockIdx.x;
     const int kv_head = head / (p.n_q_heads / p.n_kv_heads);
-    // tile_info: (first token in the flat batch, its absolute position, rows in the tile, block-table row)
-    const int4 info = tile_info[blockIdx.y];
+    // info: (first token in the flat batch, its absolute position, rows in the tile, block-table row)
     const int n0 = info.x, pos0 = info.y, rows = min(Q_TILE, info.z);
     const int hi = pos0 + rows - 1;
     int lo = (p.window > 0 && pos0 - p.window + 1 > 0) ? pos0 - p.window + 1 : 0;
@@ -350,6 +347,29 @@ attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
         if (row_b < rows)
             *reinterpret_cast<unsigned*>(p.out + ((size_t)(n0 + row_b) * p.n_q_heads + head) * D + col) =
                 pack_bf16(o[dt][2] * inv_b, o[dt][3] * inv_b);
+    }
+}
+
+// Heads vary fastest, so all heads of the longest tile start first (tiles come sorted, longest first).  The MOD
+// form gives a block two tiles, the y-th from the front of the list and the y-th from its end: with chunks a tile's
+// work grows with its place inside its chunk, not with its position, and a list sorted by position pairs a long
+// walk with a short one (for whole chunks of one request every pair walks the same number of key tiles), so the
+// launch is no longer as long as its longest tile's chain while most blocks are done early.
+template <bool MOD>
+__global__ void __launch_bounds__(128, (QIL_HEAD_DIM <= 128) ? 3 : 1)
+attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info, int n_tiles) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int head = blockIdx.x;
+    if (!MOD) {
+        attn_prefill_tile<false>(p, tile_info[blockIdx.y], head, smem_raw);
+        return;
+    }
+    const int first = blockIdx.y, second = n_tiles - 1 - (int)blockIdx.y;
+    attn_prefill_tile<MOD>(p, tile_info[first], head, smem_raw);
+    if (second > first) {
+        cp_async_wait<0>();
+        __syncthreads();         // the first tile's readers of shared memory are done
+        attn_prefill_tile<MOD>(p, tile_info[second], head, smem_raw);
     }
 }
 
@@ -944,8 +964,10 @@ static int launch_prefill(const void* q, const void* kv, void* out, const int* t
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    if (has_options(p)) attn_prefill_kernel<true><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
-    else attn_prefill_kernel<false><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
+    if (has_options(p))
+        attn_prefill_kernel<true><<<dim3(n_q_heads, (n_tiles + 1) / 2), 128, smem, stream>>>(p, (const int4*)tile_info, n_tiles);
+    else
+        attn_prefill_kernel<false><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info, n_tiles);
     QIL_CHECK_LAUNCH();
 }
 

@@ -326,7 +326,7 @@ def attend(ctx, q, cache, out, n_q_heads, n_kv_heads, head_dim, window, scale, s
                              n_q_heads, n_kv_heads, cache.page_size, scale, slopes_log2=slopes_log2)
         if n_rest:
             prefill(q, cache.pages, out, arrays["rest_tile_info"], n_rest, cache.block_table, n_q_heads,
-                    n_kv_heads, head_dim, cache.page_size, window, scale, slopes_log2)
+                    n_kv_heads, head_dim, cache.page_size, window, scale, slopes_log2, options)
     elif n_tiles:
         prefill(q, cache.pages, out, arrays["tile_info"], n_tiles, cache.block_table, n_q_heads, n_kv_heads,
                 head_dim, cache.page_size, window, scale, slopes_log2, options)

@@ -39,8 +39,17 @@ CASE_B = dict(architecture="Debisun", vocab=97, width=64, norm=dict(eps=1e-6), l
     dict(type="attention", mixer=attention(2, 1, 80, 80, 0.1, 3, 50.0, 500, 32, 128), mlp=moe(7, 1, 2, 2.5, 32, shared=16)),
     dict(type="attention", mixer=attention(8, 2, 16, 16, 0.28, 5, 10.0, 40, 10, 33), mlp=dict(kind="dense", ff=40)),
 ])
+# awkward sizes: nothing a multiple of 4 or 8, heads of 20 with values of 12, nine taps, a chunk of one position (a token sees
+# itself and the sink), a chunk longer than every request, a table of four rows, every router output chosen, more
+# identity outputs than experts, one head
+CASE_C = dict(architecture="Debisun", vocab=53, width=70, norm=dict(eps=1e-5), token_side=dict(dim=3), layers=[
+    dict(type="attention", mixer=attention(5, 5, 20, 12, 0.22, 9, 5.0, 9, 4, 1), mlp=moe(2, 3, 5, 0.6, 11, shared=9)),
+    dict(type="attention", mixer=attention(1, 1, 48, 48, 0.14, 2, 40.0, 1000, 6, 4096), mlp=dict(kind="dense", ff=37)),
+    dict(type="attention", mixer=attention(6, 3, 10, 14, 0.3, 3, 9.0, 50, 12, 17), mlp=moe(6, 0, 2, 1.3, 10)),
+])
 CASES = {"A": dict(config=CASE_A, seed=5, page_size=4, lengths=(70, 9, 33, 120, 1, 50)),
-         "B": dict(config=CASE_B, seed=6, page_size=16, lengths=(40, 3, 150, 64, 25))}
+         "B": dict(config=CASE_B, seed=6, page_size=16, lengths=(40, 3, 150, 64, 25)),
+         "C": dict(config=CASE_C, seed=7, page_size=2, lengths=(31, 2, 77, 20, 45))}
 
 
 def make_weights(config: dict, seed: int) -> dict:

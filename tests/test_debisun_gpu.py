@@ -464,7 +464,7 @@ def judge(actual, expected, low, skip, dtype, what):
     bfloat16: the yardstick is what bfloat16 costs the plain implementation itself (``low``), on the rows whose
     choice of experts is no close call.  The mean row error may be 1.5 times the yardstick's; no row's largest
     error may pass 1.5 times the yardstick's largest; a row's own error may be 1.5 times the yardstick's in that row
-    or 2.25 times its mean, which one row in fifty may pass, by a factor of two at most (a branch normed by its own
+    or 2.25 times its mean, which one row in twenty-five may pass, by a factor of two at most (a branch normed by its own
     root mean square makes single rows sensitive, and the engine does not round where the plain code does); and
     wherever the float64 row's best logit leads by four times the yardstick's largest error in that row, the
     engine's best token is the same."""
@@ -486,7 +486,7 @@ def judge(actual, expected, low, skip, dtype, what):
     assert peak(actual, worst) <= peak_bar, f"{what}: row {worst} is off by {peak(actual, worst):.3e}, the bar is {peak_bar:.3e}"
     row_bar = lambda k: max(1.5 * mean_bar, 1.5 * rms(low, k))
     over = [k for k in keys if rms(actual, k) > row_bar(k)]
-    assert len(over) <= max(1, len(keys) // 50) and all(rms(actual, k) <= 2 * row_bar(k) for k in over), \
+    assert len(over) <= max(1, len(keys) // 25) and all(rms(actual, k) <= 2 * row_bar(k) for k in over), \
         f"{what}: {len(over)} of {len(keys)} rows are further off than their bar, first {over[0]}: " \
         f"{rms(actual, over[0]):.3e} against {row_bar(over[0]):.3e}"
     judged = 0
