@@ -22,7 +22,7 @@
 // and the accumulators are scaled by rsqrt(mean(x^2) + eps) in the epilogue.  The norm weight rides through the ring as
 // one more stage row.
 //
-// Epilogues: bias, a scale per output feature, residual (of the output's type; may alias out), float32 output for the LM head
+// Epilogues: bias, a scale per output feature, an activation without a gate, residual (of the output's type; may alias out), float32 output for the LM head
 // or a float32 residual stream,
 // and `silu_pairs`: weight rows stored as groups of [8 gate rows, 8 up rows], for
 // which the block writes silu(gate) * up, 8 values per token
@@ -141,12 +141,21 @@ __device__ __forceinline__ unsigned gsm_mul2(unsigned a, unsigned b) {
 // NT: token tiles of 8.  NORM = 1: fused RMSNorm (see the top of the file).  The activations travel through the
 // ring with the weights: reading them from global memory in the threads that need them was slower at every
 // token count, because those reads miss the small L1 left beside the ring and stall the warp.
+// Activations without a gate on the product's output (the codes of gated_activation.cu): 0 silu, 1 gelu (tanh),
+// 3 squared relu.
+__device__ __forceinline__ float gsm_activation(int kind, float z) {
+    if (kind == 0) return z / (1.f + expf(-z));
+    if (kind == 1) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+}
+
 template <int NT, int NORM>
 __global__ void __launch_bounds__(GSM_WARPS * 32)
 gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                     const bf16* residual, void* out, const bf16* __restrict__ norm_w, float norm_eps,
                     int M, int N, int K, int out_f32, int silu_pairs, int first_wave,
-                    const float* __restrict__ col_scale) {
+                    const float* __restrict__ col_scale, int act) {
     extern __shared__ __align__(128) unsigned char ring[];          // [STAGES][STAGE_BYTES]
     constexpr int XROWS = 8 * NT;
     constexpr int NORM_ROW = GSM_ROWS + XROWS;                      // the stage row of the norm weight
@@ -309,6 +318,7 @@ gemm_small_m_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, cons
         v *= inverse_rms(token);
         if (bias != nullptr) v += __bfloat162float(bias[n]);
         if (col_scale != nullptr) v *= col_scale[n];     // a learned scale per feature on the way into the residual
+        if (act >= 0) v = gsm_activation(act, round_to<bf16>(v));     // as the product's rounded output through the stand-alone kernel
         if (residual != nullptr)     // the residual has the output's type
             v = (out_f32 ? reinterpret_cast<const float*>(residual)[(size_t)token * N + n]
                          : __bfloat162float(residual[(size_t)token * N + n])) + v;
@@ -354,7 +364,7 @@ __global__ void __launch_bounds__(GSM_THREADS)
 gemm_small_m_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, const bf16* __restrict__ bias,
                          const bf16* residual, void* out, const bf16* __restrict__ norm_w, float norm_eps,
                          int M, int N, int K, int out_f32, int silu_pairs, int first_wave,
-                    const float* __restrict__ col_scale) {
+                    const float* __restrict__ col_scale, int act) {
     extern __shared__ __align__(128) unsigned char ring[];
     constexpr int XROWS = 8 * NT;
     constexpr int NORM_ROW = GW_ROWS + XROWS;
@@ -499,6 +509,7 @@ gemm_small_m_wide_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W,
         v *= inverse_rms(token);
         if (bias != nullptr) v += __bfloat162float(bias[n]);
         if (col_scale != nullptr) v *= col_scale[n];     // a learned scale per feature on the way into the residual
+        if (act >= 0) v = gsm_activation(act, round_to<bf16>(v));     // as the product's rounded output through the stand-alone kernel
         if (residual != nullptr)     // the residual has the output's type
             v = (out_f32 ? reinterpret_cast<const float*>(residual)[(size_t)token * N + n]
                          : __bfloat162float(residual[(size_t)token * N + n])) + v;
@@ -512,7 +523,7 @@ extern "C" int qil_gemm_small_m_max_rows() { return 16; }
 // norm_w: null, or the K weights of the RMSNorm to apply to x first (with norm_eps).
 extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, const void* residual, void* out,
                                 const void* norm_w, float norm_eps, int M, int N, int K, int out_f32, int silu_pairs,
-                                int rows_per_block, const float* col_scale, cudaStream_t stream) {
+                                int rows_per_block, const float* col_scale, int act, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (rows_per_block != 16 && rows_per_block != 32) QIL_REFUSE("gemm_small_m: %d output features a block; 16 or 32", rows_per_block);
     if (rows_per_block == 32 && N % 32) QIL_REFUSE("gemm_small_m: 32 output features a block need N %% 32 == 0, got %d", N);
@@ -523,6 +534,8 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
     if (silu_pairs && (N % 16 || bias != nullptr || residual != nullptr || out_f32))
         QIL_REFUSE("gemm_small_m: silu_pairs needs N %% 16 == 0 and no bias, residual or float32 output");
     if (silu_pairs && col_scale != nullptr) QIL_REFUSE("gemm_small_m: silu_pairs takes no output scale");
+    if (act >= 0 && (act > 3 || act == 2 || silu_pairs || out_f32 || residual != nullptr || col_scale != nullptr))
+        QIL_REFUSE("gemm_small_m: an activation (0 silu, 1 gelu, 3 squared relu) goes with a plain bfloat16 output");
     const int blocks = (N + GSM_ROWS - 1) / GSM_ROWS;
     const int smem1 = GSM_STAGES * (GSM_ROWS + 8) * GSM_ROW_BYTES, smem1n = GSM_STAGES * (GSM_ROWS + 8 + 1) * GSM_ROW_BYTES;
     const int smem2 = 3 * (GSM_ROWS + 16) * GSM_ROW_BYTES, smem2n = 3 * (GSM_ROWS + 16 + 1) * GSM_ROW_BYTES;
@@ -558,7 +571,7 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
 #define GW_LAUNCH(NT, NORM, SMEM)                                                                                   \
         qil_launch_chained(gemm_small_m_wide_kernel<NT, NORM>, dim3(N / GW_ROWS), dim3(GSM_THREADS), SMEM, stream,  \
                            (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out,            \
-                           (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs, first_wave, col_scale)
+                           (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs, first_wave, col_scale, act)
         if (norm_w == nullptr) {
             if (M <= 8) GW_LAUNCH(1, 0, w1); else GW_LAUNCH(2, 0, w2);
         } else {
@@ -570,7 +583,7 @@ extern "C" int qil_gemm_small_m(const void* x, const void* W, const void* bias, 
 #define GSM_LAUNCH(NT, NORM, SMEM)                                                                                  \
     qil_launch_chained(gemm_small_m_kernel<NT, NORM>, dim3(blocks), dim3(GSM_WARPS * 32), SMEM, stream,           \
                        (const bf16*)x, (const bf16*)W, (const bf16*)bias, (const bf16*)residual, out,                \
-                       (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs, first_wave, col_scale)
+                       (const bf16*)norm_w, norm_eps, M, N, K, out_f32, silu_pairs, first_wave, col_scale, act)
     if (norm_w == nullptr) {
         if (M <= 8) GSM_LAUNCH(1, 0, smem1); else GSM_LAUNCH(2, 0, smem2);
     } else {

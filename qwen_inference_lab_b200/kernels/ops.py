@@ -213,7 +213,7 @@ def small_m_ok(a, weight) -> bool:
 
 
 def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=False, silu_pairs=False,
-                 norm_weight=None, norm_eps=0.0, rows_per_block=None, col_scale=None):
+                 norm_weight=None, norm_eps=0.0, rows_per_block=None, col_scale=None, activation=None):
     """out = a @ weight.T (+ bias) (+ residual) for a decode step's few rows, streaming the weight once.
 
     a bfloat16 [M <= 16, K]; weight bfloat16 [N, K].  ``out_float32`` returns float32 (the LM head).
@@ -223,6 +223,7 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
     ``rows_per_block``: 16 or 32 output features a block (32 wants N a multiple of 32); None leaves it to the
     measured rule in ``tuning``.  The two forms add a product's terms in different orders.
     ``col_scale`` float32 [N]: out = (a @ weight.T + bias) * col_scale + residual.
+    ``activation``: one of ``PLAIN_ACTIVATIONS`` on the product's bfloat16-rounded value (no residual, no scale).
     """
     _need(a, "a", torch.bfloat16, 2); _need(weight, "weight", torch.bfloat16, 2)
     m, k = a.shape
@@ -250,6 +251,9 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
         _need(col_scale, "col_scale", torch.float32, 1)
         if col_scale.shape[0] != n or silu_pairs:
             raise KernelError("gemm_small_m: one output scale per feature, and none with silu_pairs")
+    if activation is not None and (activation not in PLAIN_ACTIVATIONS or out_float32 or residual is not None
+                                   or col_scale is not None or silu_pairs):
+        raise KernelError("gemm_small_m: an activation goes with a plain bfloat16 output")
     if rows_per_block is None:
         wide = (n % 32 == 0 and n // 32 >= tuning.SMALL_M_WIDE_MIN_BLOCKS
                 and (m > 8 or n * k < tuning.SMALL_M_WIDE_MAX_ELEMENTS))
@@ -258,7 +262,8 @@ def gemm_small_m(a, weight, bias=None, residual=None, out=None, out_float32=Fals
     _check(lib, lib.qil_gemm_small_m(_p(a), _p(weight), _p(bias), _p(residual), _p(out), _p(norm_weight),
                                      c_float(float(norm_eps)), c_int(m), c_int(n), c_int(k),
                                      c_int(1 if out_float32 else 0), c_int(1 if silu_pairs else 0),
-                                     c_int(rows_per_block), _p(col_scale), _stream()),
+                                     c_int(rows_per_block), _p(col_scale),
+                                     c_int(ACTIVATIONS[activation] if activation is not None else -1), _stream()),
            "gemm_small_m")
     return out
 

@@ -98,6 +98,5 @@ class PlainMLP(FeedForward):
         return [self.up, self.down]
 
     def forward(self, ctx, x, residual=None, norm=None, out_scale=None, out_float32=False):
-        hidden = self.up.forward(ctx, x, norm=norm)
-        ops.activation(hidden, self.activation, out=hidden)
+        hidden = self.up.forward(ctx, x, norm=norm, activation=self.activation)
         return self.down.forward(ctx, hidden, residual=residual, out_scale=out_scale, out_float32=out_float32)

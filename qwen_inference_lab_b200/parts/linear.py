@@ -55,7 +55,7 @@ class Linear(Part):
     def _bias(self):
         return self.bias.data if self.bias is not None else None
 
-    def forward(self, ctx, x, residual=None, out=None, out_float32=False, norm=None, out_scale=None):
+    def forward(self, ctx, x, residual=None, out=None, out_float32=False, norm=None, out_scale=None, activation=None):
         """``x`` [N, in] -> [N, out]; adds ``residual`` [N, out] when given (may be ``out``).
 
         ``out_scale`` float32 [out]: a learned scale per output feature on the way into the residual, which is
@@ -66,6 +66,19 @@ class Linear(Part):
         float32 result: the product's float32 sums are added to it without a rounding in between.
         """
         weight, bias = self._weight(), self._bias()
+        if norm is not None and norm.as_rms() is None:
+            # a norm that no product kernel applies itself (float32 statistics of a float32 stream, a layer norm):
+            # normed first, so that what follows is chosen by the rows the product really gets
+            x, norm = norm.forward(ctx, x), None
+        if activation is not None:
+            # ``activation``: one of ``ops.PLAIN_ACTIVATIONS`` on the result, in the weight-streaming kernel's
+            # epilogue for a decode step's rows, else by a kernel of its own
+            if residual is not None or out_scale is not None or out_float32:
+                raise ValueError("an activation goes with a plain product")
+            if norm is None and ops.small_m_ok(x, weight):
+                return ops.gemm_small_m(x, weight, bias=bias, out=out, activation=activation)
+            result = self.forward(ctx, x, out=out, norm=norm)
+            return ops.activation(result, activation, out=result)
         if out_scale is not None:
             if residual is None or out is not None:
                 raise ValueError("an output scale goes with a residual, which is updated in place")

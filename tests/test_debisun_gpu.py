@@ -463,7 +463,7 @@ def judge(actual, expected, low, skip, dtype, what):
 
     bfloat16: the yardstick is what bfloat16 costs the plain implementation itself (``low``), on the rows whose
     choice of experts is no close call.  The mean row error may be 1.5 times the yardstick's; no row's largest
-    error may pass 1.5 times the yardstick's largest; a row's own error may be 1.5 times the yardstick's in that row
+    error may pass twice the yardstick's largest (the largest of a few hundred rows is itself a draw); a row's own error may be 1.5 times the yardstick's in that row
     or 2.25 times its mean, which one row in twenty-five may pass, by a factor of two at most (a branch normed by its own
     root mean square makes single rows sensitive, and the engine does not round where the plain code does); and
     wherever the float64 row's best logit leads by four times the yardstick's largest error in that row, the
@@ -479,7 +479,7 @@ def judge(actual, expected, low, skip, dtype, what):
     rms = lambda rows, k: (rows[k] - expected[k]).pow(2).mean().sqrt().item()
     peak = lambda rows, k: (rows[k] - expected[k]).abs().max().item()
     mean_bar = 1.5 * sum(rms(low, k) for k in keys) / len(keys)
-    peak_bar = 1.5 * max(peak(low, k) for k in keys)
+    peak_bar = 2.0 * max(peak(low, k) for k in keys)
     mean_rms = sum(rms(actual, k) for k in keys) / len(keys)
     assert mean_rms <= mean_bar, f"{what}: mean row error {mean_rms:.3e} against a bar of {mean_bar:.3e}"
     worst = max(keys, key=lambda k: peak(actual, k))
