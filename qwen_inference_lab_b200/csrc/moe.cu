@@ -50,59 +50,12 @@ __device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
     for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(pairs[j]); v[2 * j] = f.x; v[2 * j + 1] = f.y; }
 }
 
-template <typename T, typename W>
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W* __restrict__ bias, int width,
-                 int n_outputs, int top, int* __restrict__ chosen, float* __restrict__ weights, int mode,
-                 const float* __restrict__ correction, float weight_scale, float* __restrict__ gate_logit) {
-    __shared__ float logits[MOE_MAX_EXPERTS];
-    __shared__ float choice[MOE_MAX_EXPERTS];
-    const int n_experts = n_outputs + (gate_logit != nullptr ? 1 : 0);     // rows of `router` (the gate's row is the last)
-    __shared__ float sel_p[MOE_MAX_TOP];
-    __shared__ int sel_at[MOE_MAX_TOP];
-    qil_wait_for_producer();
-    qil_release_consumer();
-    const size_t token = blockIdx.x;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const T* row = x + token * width;
-    // A lane takes runs of 8 values, 16 or 32 bytes a load, four runs in flight per operand; its partial sum runs in
-    // ascending order, the lanes' sums meet in a fixed tree: the same bits whatever else is in the batch.
-    const bool wide = width % 8 == 0 && (((uintptr_t)x | (uintptr_t)router) & 15) == 0;
-    const int warps = blockDim.x >> 5;
-    if (wide) {
-        // four experts at a time share every load of the token's row and keep four weight loads in flight
-        for (int e0 = warp * 4; e0 < n_experts; e0 += warps * 4) {
-            float dot[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 2
-            for (int i = lane * 8; i < width; i += 256) {
-                float a[8];
-                load8(row + i, a);
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (e0 + u >= n_experts) continue;
-                    float b[8];
-                    load8(router + (size_t)(e0 + u) * width + i, b);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) dot[u] = fmaf(a[j], b[j], dot[u]);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float total = warp_sum(dot[u]);
-                if (lane == 0 && e0 + u < n_experts) logits[e0 + u] = total + (bias != nullptr ? to_f32<W>(bias[e0 + u]) : 0.f);
-            }
-        }
-    } else {
-        for (int e = warp; e < n_experts; e += warps) {
-            const W* w = router + (size_t)e * width;
-            float dot = 0.f;
-            for (int i = lane; i < width; i += 32) dot = fmaf(to_f32<T>(row[i]), to_f32<W>(w[i]), dot);
-            dot = warp_sum(dot);
-            if (lane == 0) logits[e] = dot + (bias != nullptr ? to_f32<W>(bias[e]) : 0.f);
-        }
-    }
-    __syncthreads();
-    if (warp != 0) return;
+// One warp: from a token's logits in shared memory to its chosen outputs and their weights (both modes; see the
+// file's head).  `logits`, `choice`, `sel_p`, `sel_at` are this token's own arrays.
+__device__ __forceinline__ void moe_select(float* logits, float* choice, float* sel_p, int* sel_at, size_t token,
+                                           int n_outputs, int top, int* __restrict__ chosen, float* __restrict__ weights,
+                                           int mode, const float* __restrict__ correction, float weight_scale,
+                                           float* __restrict__ gate_logit, int lane) {
     if (gate_logit != nullptr) {
         if (lane == 0) gate_logit[token] = logits[n_outputs];
     }
@@ -177,6 +130,118 @@ moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W*
         chosen[token * top + k] = sel_at[k];
         weights[token * top + k] = total > 0.f ? sel_p[k] / total : 0.f;
     }
+}
+
+// The same for many tokens: a block takes MOE_ROUTE_TOKENS tokens, and a warp's four router rows at a time serve all of
+// them, so the router is read from L2 a quarter as often.  Every dot product is summed exactly as in the kernel below
+// (the same runs per lane, the same tree): a token's logits are the same bits whichever kernel takes it.
+#define MOE_ROUTE_TOKENS 4
+template <typename T, typename W>
+__global__ void __launch_bounds__(256)
+moe_route_tile_kernel(const T* __restrict__ x, const W* __restrict__ router, const W* __restrict__ bias, int n_tokens,
+                      int width, int n_outputs, int top, int* __restrict__ chosen, float* __restrict__ weights, int mode,
+                      const float* __restrict__ correction, float weight_scale, float* __restrict__ gate_logit) {
+    __shared__ float logits[MOE_ROUTE_TOKENS][MOE_MAX_EXPERTS];
+    __shared__ float choice[MOE_ROUTE_TOKENS][MOE_MAX_EXPERTS];
+    __shared__ float sel_p[MOE_ROUTE_TOKENS][MOE_MAX_TOP];
+    __shared__ int sel_at[MOE_ROUTE_TOKENS][MOE_MAX_TOP];
+    const int n_experts = n_outputs + (gate_logit != nullptr ? 1 : 0);
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const int token0 = blockIdx.x * MOE_ROUTE_TOKENS;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    for (int e0 = warp * 4; e0 < n_experts; e0 += warps * 4) {
+        float dot[MOE_ROUTE_TOKENS][4];
+#pragma unroll
+        for (int t = 0; t < MOE_ROUTE_TOKENS; ++t) dot[t][0] = dot[t][1] = dot[t][2] = dot[t][3] = 0.f;
+        for (int i = lane * 8; i < width; i += 256) {
+            float b[4][8];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (e0 + u < n_experts) load8(router + (size_t)(e0 + u) * width + i, b[u]);
+#pragma unroll
+            for (int t = 0; t < MOE_ROUTE_TOKENS; ++t) {
+                if (token0 + t >= n_tokens) continue;
+                float a[8];
+                load8(x + (size_t)(token0 + t) * width + i, a);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (e0 + u >= n_experts) continue;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dot[t][u] = fmaf(a[j], b[u][j], dot[t][u]);
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < MOE_ROUTE_TOKENS; ++t)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float total = warp_sum(dot[t][u]);
+                if (lane == 0 && e0 + u < n_experts)
+                    logits[t][e0 + u] = total + (bias != nullptr ? to_f32<W>(bias[e0 + u]) : 0.f);
+            }
+    }
+    __syncthreads();
+    if (warp >= MOE_ROUTE_TOKENS || token0 + warp >= n_tokens) return;
+    moe_select(logits[warp], choice[warp], sel_p[warp], sel_at[warp], (size_t)(token0 + warp), n_outputs, top, chosen, weights,
+               mode, correction, weight_scale, gate_logit, lane);
+}
+
+template <typename T, typename W>
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const T* __restrict__ x, const W* __restrict__ router, const W* __restrict__ bias, int width,
+                 int n_outputs, int top, int* __restrict__ chosen, float* __restrict__ weights, int mode,
+                 const float* __restrict__ correction, float weight_scale, float* __restrict__ gate_logit) {
+    __shared__ float logits[MOE_MAX_EXPERTS];
+    __shared__ float choice[MOE_MAX_EXPERTS];
+    const int n_experts = n_outputs + (gate_logit != nullptr ? 1 : 0);     // rows of `router` (the gate's row is the last)
+    __shared__ float sel_p[MOE_MAX_TOP];
+    __shared__ int sel_at[MOE_MAX_TOP];
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const size_t token = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const T* row = x + token * width;
+    // A lane takes runs of 8 values, 16 or 32 bytes a load, four runs in flight per operand; its partial sum runs in
+    // ascending order, the lanes' sums meet in a fixed tree: the same bits whatever else is in the batch.
+    const bool wide = width % 8 == 0 && (((uintptr_t)x | (uintptr_t)router) & 15) == 0;
+    const int warps = blockDim.x >> 5;
+    if (wide) {
+        // four experts at a time share every load of the token's row and keep four weight loads in flight
+        for (int e0 = warp * 4; e0 < n_experts; e0 += warps * 4) {
+            float dot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+            for (int i = lane * 8; i < width; i += 256) {
+                float a[8];
+                load8(row + i, a);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (e0 + u >= n_experts) continue;
+                    float b[8];
+                    load8(router + (size_t)(e0 + u) * width + i, b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) dot[u] = fmaf(a[j], b[j], dot[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float total = warp_sum(dot[u]);
+                if (lane == 0 && e0 + u < n_experts) logits[e0 + u] = total + (bias != nullptr ? to_f32<W>(bias[e0 + u]) : 0.f);
+            }
+        }
+    } else {
+        for (int e = warp; e < n_experts; e += warps) {
+            const W* w = router + (size_t)e * width;
+            float dot = 0.f;
+            for (int i = lane; i < width; i += 32) dot = fmaf(to_f32<T>(row[i]), to_f32<W>(w[i]), dot);
+            dot = warp_sum(dot);
+            if (lane == 0) logits[e] = dot + (bias != nullptr ? to_f32<W>(bias[e]) : 0.f);
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    moe_select(logits, choice, sel_p, sel_at, token, n_outputs, top, chosen, weights, mode, correction, weight_scale,
+               gate_logit, lane);
 }
 
 // ------------------------------------------------------------------ group
@@ -571,6 +636,57 @@ moe_combine_kernel(const float* __restrict__ y, const R* __restrict__ residual, 
     }
 }
 
+// The same for a float32 stream whose width is a multiple of 4: a block walks rows, a thread four columns of each,
+// 16 bytes a load, no division per element.  The sums are those of the kernel above, slot by slot.
+__device__ __forceinline__ float4 moe_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 moe_load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_f32x4_kernel(const float* __restrict__ y, const float* __restrict__ residual, float* __restrict__ out,
+                         int n_tokens, int width, int top, CombineExtras ex) {
+    qil_wait_for_producer();
+    qil_release_consumer();
+    const T* x = reinterpret_cast<const T*>(ex.x);
+    for (int token = blockIdx.x; token < n_tokens; token += gridDim.x) {
+        const float gate = (ex.extra != nullptr && ex.gate_logit != nullptr) ? 1.f / (1.f + expf(-ex.gate_logit[token])) : 1.f;
+        for (int col = threadIdx.x * 4; col < width; col += 1024) {
+            const size_t i = (size_t)token * width + col;
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < top; ++s) {
+                const size_t pair = (size_t)token * top + s;
+                float4 v;
+                if (x != nullptr && ex.chosen[pair] >= ex.n_experts) {
+                    const float w = ex.weights[pair];
+                    v = moe_load4(x + i);
+                    v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+                } else {
+                    v = moe_load4(y + pair * width + col);
+                }
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+            }
+            if (ex.extra != nullptr) {
+                const float4 v = moe_load4(ex.extra + i);
+                sum.x += gate * v.x; sum.y += gate * v.y; sum.z += gate * v.z; sum.w += gate * v.w;
+            }
+            if (ex.col_scale != nullptr) {
+                const float4 c = moe_load4(ex.col_scale + col);
+                sum.x *= c.x; sum.y *= c.y; sum.z *= c.z; sum.w *= c.w;
+            }
+            if (residual != nullptr) {
+                const float4 r = moe_load4(residual + i);
+                sum.x = r.x + sum.x; sum.y = r.y + sum.y; sum.z = r.z + sum.z; sum.w = r.w + sum.w;
+            }
+            *reinterpret_cast<float4*>(out + i) = sum;
+        }
+    }
+}
+
 // ------------------------------------------------------------------ entry points
 // `router` holds n_experts rows, and one more behind them when `gate_logit` is given.
 extern "C" int qil_moe_route(const void* x, const void* router, const void* bias, int n_tokens, int width,
@@ -583,6 +699,13 @@ extern "C" int qil_moe_route(const void* x, const void* router, const void* bias
         QIL_REFUSE("moe_route: %d experts (at most %d), %d of them per token, width %d", n_experts, MOE_MAX_EXPERTS, top, width);
     if (mode != 0 && mode != 1) QIL_REFUSE("moe_route: mode %d", mode);
     if (gate_logit != nullptr && bias != nullptr) QIL_REFUSE("moe_route: a gate row goes without router biases");
+    if (n_tokens >= 64 && width % 8 == 0 && (((uintptr_t)x | (uintptr_t)router) & 15) == 0) {
+        QIL_DISPATCH_2(act_dtype, weight_dtype,
+            qil_launch_chained(moe_route_tile_kernel<T, W>, dim3((n_tokens + MOE_ROUTE_TOKENS - 1) / MOE_ROUTE_TOKENS), dim3(256),
+                               0, stream, (const T*)x, (const W*)router, (const W*)bias, n_tokens, width, n_experts, top, chosen,
+                               weights, mode, correction, weight_scale, gate_logit));
+        QIL_CHECK_LAUNCH();
+    }
     QIL_DISPATCH_2(act_dtype, weight_dtype,
         qil_launch_chained(moe_route_kernel<T, W>, dim3(n_tokens), dim3(256), 0, stream, (const T*)x, (const W*)router,
                            (const W*)bias, width, n_experts, top, chosen, weights, mode, correction, weight_scale,
@@ -676,6 +799,17 @@ extern "C" int qil_moe_combine(const float* y, const void* residual, void* out, 
     const size_t total = (size_t)n_tokens * width;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     CombineExtras ex = {chosen, weights, x, n_experts, extra, gate_logit, col_scale};
+    if (stream_dtype == QIL_F32 && width % 4 == 0
+        && (((uintptr_t)y | (uintptr_t)residual | (uintptr_t)out | (uintptr_t)x | (uintptr_t)extra | (uintptr_t)col_scale) & 15) == 0) {
+        const int rows = n_tokens < 148 * 8 ? n_tokens : 148 * 8;
+        if (x_dtype == QIL_BF16)
+            qil_launch_chained(moe_combine_f32x4_kernel<bf16>, dim3(rows), dim3(256), 0, stream, y, (const float*)residual,
+                               (float*)out, n_tokens, width, top, ex);
+        else
+            qil_launch_chained(moe_combine_f32x4_kernel<float>, dim3(rows), dim3(256), 0, stream, y, (const float*)residual,
+                               (float*)out, n_tokens, width, top, ex);
+        QIL_CHECK_LAUNCH();
+    }
     // R: the stream's type, T: the input rows' type
     QIL_DISPATCH_2(x_dtype, stream_dtype,
         qil_launch_chained(moe_combine_kernel<W, T>, dim3(blocks), dim3(256), 0, stream, y, (const W*)residual, (W*)out,
