@@ -157,7 +157,7 @@ __device__ __forceinline__ void issue_kv_tile(const AttnParams& p, const int* ro
 }
 
 // ------------------------------------------------------------------ prompt portions
-// One query tile of one head: the whole of a block's work in the plain form, half of it in the MOD form.
+// One query tile of one head: a block's work.
 template <bool MOD>
 __device__ __forceinline__ void attn_prefill_tile(const AttnParams& p, const int4 info, const int head,
                                                   unsigned char* smem_raw) {
@@ -350,27 +350,12 @@ __device__ __forceinline__ void attn_prefill_tile(const AttnParams& p, const int
     }
 }
 
-// Heads vary fastest, so all heads of the longest tile start first (tiles come sorted, longest first).  The MOD
-// form gives a block two tiles, the y-th from the front of the list and the y-th from its end: with chunks a tile's
-// work grows with its place inside its chunk, not with its position, and a list sorted by position pairs a long
-// walk with a short one (for whole chunks of one request every pair walks the same number of key tiles), so the
-// launch is no longer as long as its longest tile's chain while most blocks are done early.
+// Heads vary fastest, so all heads of the longest tile start first (tiles come sorted, longest first).
 template <bool MOD>
 __global__ void __launch_bounds__(128, (QIL_HEAD_DIM <= 128) ? 3 : 1)
-attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info, int n_tiles) {
+attn_prefill_kernel(AttnParams p, const int4* __restrict__ tile_info) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int head = blockIdx.x;
-    if (!MOD) {
-        attn_prefill_tile<false>(p, tile_info[blockIdx.y], head, smem_raw);
-        return;
-    }
-    const int first = blockIdx.y, second = n_tiles - 1 - (int)blockIdx.y;
-    attn_prefill_tile<MOD>(p, tile_info[first], head, smem_raw);
-    if (second > first) {
-        cp_async_wait<0>();
-        __syncthreads();         // the first tile's readers of shared memory are done
-        attn_prefill_tile<MOD>(p, tile_info[second], head, smem_raw);
-    }
+    attn_prefill_tile<MOD>(p, tile_info[blockIdx.y], (int)blockIdx.x, smem_raw);
 }
 
 // ------------------------------------------------------------------ single tokens: how long a span
@@ -964,10 +949,8 @@ static int launch_prefill(const void* q, const void* kv, void* out, const int* t
         if (e != cudaSuccess) QIL_REFUSE("attention: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    if (has_options(p))
-        attn_prefill_kernel<true><<<dim3(n_q_heads, (n_tiles + 1) / 2), 128, smem, stream>>>(p, (const int4*)tile_info, n_tiles);
-    else
-        attn_prefill_kernel<false><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info, n_tiles);
+    if (has_options(p)) attn_prefill_kernel<true><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
+    else attn_prefill_kernel<false><<<dim3(n_q_heads, n_tiles), 128, smem, stream>>>(p, (const int4*)tile_info);
     QIL_CHECK_LAUNCH();
 }
 
